@@ -1,0 +1,232 @@
+// C ABI entry points: argument validation, launch geometry and dispatch.  No allocation, no
+// synchronisation, no device-property query on the launch path (the SM count is cached per
+// device on first use), so every call can be captured into a CUDA graph.
+#include <atomic>
+#include <mutex>
+
+#include "bhi_common.cuh"
+#include "bhi_encode.cuh"
+#include "bhi_generic.cuh"
+#include "bhi_staged.cuh"
+
+namespace bhi {
+
+static thread_local std::string g_error;
+static std::atomic<int> g_path{0};
+
+void set_error(const std::string &msg) { g_error = msg; }
+int fail(int code, const std::string &msg) {
+    g_error = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char *what) {
+    g_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return BHI_ERR_CUDA;
+}
+
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+static int check_layer(const void *rem, const void *exp, int64_t exp_words, const void *offsets,
+                       int S, int M, int Nc) {
+    BHI_REQUIRE(rem && exp && offsets, "null weight buffer");
+    BHI_REQUIRE(S >= 1 && M >= 1, "empty layer");
+    BHI_REQUIRE(Nc >= 128 && Nc % 128 == 0 && Nc <= 16384, "chunk width must be a multiple of 128 in [128, 16384]");
+    BHI_REQUIRE(exp_words >= 64, "exponent buffer shorter than one record row");
+    BHI_REQUIRE(aligned(rem, 4) && aligned(exp, 4) && aligned(offsets, 4), "weight buffers must be 4-byte aligned");
+    return BHI_OK;
+}
+
+static int launch_status(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BHI_OK : cuda_fail(e, what);
+}
+
+template <class Codec>
+static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uint16_t *X, uint16_t *Y, int B,
+                    cudaStream_t st) {
+    BHI_REQUIRE(X && Y, "null activation buffer");
+    BHI_REQUIRE(B >= 1 && B <= BHI_MAX_BATCH, "batch must be in [1, 8]");
+    BHI_REQUIRE(aligned(X, 4) && aligned(Y, 2), "activation buffers must be 4-byte (X) / 2-byte (Y) aligned");
+    if (g_path.load() == 0) {
+        int rc = staged_gemv<Codec>(L, targs, X, Y, B, st);
+        if (rc != kStagedDeclined) return rc;
+    }
+    // one warp per row, enough blocks to give every row its own warp up to 8 waves of blocks per SM
+    const int warps_per_block = kGenericThreads / 32;
+    int blocks = (L.M + warps_per_block - 1) / warps_per_block;
+    const int cap = sm_count() * 64;
+    if (blocks > cap) blocks = cap;
+#define BHI_CASE(b)                                                                                  \
+    case b:                                                                                          \
+        gemv_generic_kernel<Codec, b><<<blocks, kGenericThreads, 0, st>>>(L, targs, X, Y);           \
+        break;
+    switch (B) {
+        BHI_CASE(1) BHI_CASE(2) BHI_CASE(3) BHI_CASE(4) BHI_CASE(5) BHI_CASE(6) BHI_CASE(7) BHI_CASE(8)
+    }
+#undef BHI_CASE
+    return launch_status("gemv launch");
+}
+
+template <class Codec>
+static int run_decode(const Layer &L, const typename Codec::Args &targs, uint16_t *Y, cudaStream_t st) {
+    BHI_REQUIRE(Y, "null output buffer");
+    BHI_REQUIRE(aligned(Y, 4), "output must be 4-byte aligned");
+    if (g_path.load() == 0) {
+        int rc = staged_decode<Codec>(L, targs, Y, st);
+        if (rc != kStagedDeclined) return rc;
+    }
+    const int64_t nrec = static_cast<int64_t>(L.S) * L.M;
+    const int warps_per_block = kGenericThreads / 32;
+    int64_t blocks = (nrec + warps_per_block - 1) / warps_per_block;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 64;
+    if (blocks > cap) blocks = cap;
+    decode_generic_kernel<Codec><<<static_cast<int>(blocks), kGenericThreads, 0, st>>>(L, targs, Y);
+    return launch_status("decode launch");
+}
+
+static int check_enc(const void *W, int M, int K, int S) {
+    BHI_REQUIRE(W, "null weight");
+    BHI_REQUIRE(M >= 1 && K >= 128 && S >= 1 && K % S == 0, "bad shape");
+    const int Nc = K / S;
+    BHI_REQUIRE(Nc % 128 == 0 && Nc <= 16384, "chunk width must be a multiple of 128, at most 16384");
+    BHI_REQUIRE(aligned(W, 4), "weight must be 4-byte aligned");
+    return BHI_OK;
+}
+
+static int enc_blocks(int M, int S) {
+    return static_cast<int>((static_cast<int64_t>(S) * M + kEncRecords - 1) / kEncRecords);
+}
+
+}  // namespace bhi
+
+using namespace bhi;
+
+extern "C" {
+
+const char *bhi_last_error(void) { return g_error.c_str(); }
+int bhi_abi_version(void) { return 1; }
+int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
+
+int bhi_gemv_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                          const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                          const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                          const uint8_t *LUT4, const uint8_t *code_lengths,
+                          int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths, "null table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
+    return run_gemv<HuffCodec>(L, t, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                       uint16_t *Y, const int32_t *offsets,
+                       const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                       const uint8_t *LUT4, const uint8_t *code_lengths,
+                       int split_k, int M, int Nc, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths, "null table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
+    return run_decode<HuffCodec>(L, t, Y, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                      int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    AnsArgs t{LUT};
+    return run_gemv<AnsCodec>(L, t, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                   int split_k, int M, int Nc, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    AnsArgs t{LUT};
+    return run_decode<AnsCodec>(L, t, Y, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_huffman_encode(const uint8_t *data, int streams, int n, const uint8_t *LUT,
+                       uint8_t *output, int32_t *output_lengths, void *stream) {
+    BHI_REQUIRE(data && LUT && output && output_lengths, "null buffer");
+    BHI_REQUIRE(streams >= 0 && n >= 0, "negative size");
+    if (streams == 0) return BHI_OK;
+    const int threads = 128;
+    huffman_encode_chars_kernel<<<(streams + threads - 1) / threads, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        data, streams, n, LUT, output, output_lengths);
+    return launch_status("huffman_encode launch");
+}
+
+int bhi_ans_encode(const uint8_t *data, int streams, int n, const uint32_t *freq,
+                   const uint32_t *cum, uint32_t *output, int32_t *output_lengths, void *stream) {
+    BHI_REQUIRE(data && freq && cum && output && output_lengths, "null buffer");
+    BHI_REQUIRE(streams >= 0 && n >= 0, "negative size");
+    if (streams == 0) return BHI_OK;
+    const int threads = 128;
+    ans_encode_words_kernel<<<(streams + threads - 1) / threads, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        data, streams, n, freq, cum, output, output_lengths);
+    return launch_status("ans_encode launch");
+}
+
+int bhi_huffman_size_pass(const uint16_t *W, int M, int K, int split_k, const uint8_t *code_lengths,
+                          int32_t *words_per_row, void *stream) {
+    if (int rc = check_enc(W, M, K, split_k)) return rc;
+    BHI_REQUIRE(code_lengths && words_per_row, "null buffer");
+    EncGeom g{W, M, K, split_k, K / split_k};
+    huffman_size_kernel<<<enc_blocks(M, split_k), kEncThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, code_lengths, words_per_row);
+    return launch_status("huffman size pass launch");
+}
+
+int bhi_ans_size_pass(const uint16_t *W, int M, int K, int split_k, const uint32_t *freq,
+                      const uint32_t *cum, int32_t *words_per_row, uint8_t *stream_words, void *stream) {
+    if (int rc = check_enc(W, M, K, split_k)) return rc;
+    BHI_REQUIRE(freq && cum && words_per_row && stream_words, "null buffer");
+    EncGeom g{W, M, K, split_k, K / split_k};
+    ans_size_kernel<<<enc_blocks(M, split_k), kEncThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, freq, cum, words_per_row, stream_words);
+    return launch_status("rANS size pass launch");
+}
+
+int bhi_huffman_emit_pass(const uint16_t *W, int M, int K, int split_k, const uint8_t *code_lengths,
+                          const uint32_t *code_values, const int32_t *offsets,
+                          uint8_t *A_rem, uint32_t *A_exp, void *stream) {
+    if (int rc = check_enc(W, M, K, split_k)) return rc;
+    BHI_REQUIRE(code_lengths && code_values && offsets && A_rem && A_exp, "null buffer");
+    BHI_REQUIRE(aligned(A_rem, 2) && aligned(A_exp, 4), "unaligned output");
+    EncGeom g{W, M, K, split_k, K / split_k};
+    huffman_emit_kernel<<<enc_blocks(M, split_k), kEncThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, code_lengths, code_values, offsets, A_rem, A_exp);
+    return launch_status("huffman emit pass launch");
+}
+
+int bhi_ans_emit_pass(const uint16_t *W, int M, int K, int split_k, const uint32_t *freq,
+                      const uint32_t *cum, const int32_t *offsets, const uint8_t *stream_words,
+                      uint8_t *A_rem, uint32_t *A_exp, void *stream) {
+    if (int rc = check_enc(W, M, K, split_k)) return rc;
+    BHI_REQUIRE(freq && cum && offsets && stream_words && A_rem && A_exp, "null buffer");
+    BHI_REQUIRE(aligned(A_rem, 2) && aligned(A_exp, 4), "unaligned output");
+    EncGeom g{W, M, K, split_k, K / split_k};
+    ans_emit_kernel<<<enc_blocks(M, split_k), kEncThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, freq, cum, offsets, stream_words, A_rem, A_exp);
+    return launch_status("rANS emit pass launch");
+}
+
+}  // extern "C"

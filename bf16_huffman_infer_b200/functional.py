@@ -1,0 +1,421 @@
+"""Compressed-weight containers, the ``F.linear`` hook and model surgery.
+
+Public surface and behaviour follow the reference's ``bf16_huffman_infer/functional.py``
+(``HuffmanWeight`` :66-242, ``ANSWeight`` :245-310, ``CompressedLinear`` :313-320, ``convert``
+:323-375, ``convert_all_linear`` :378-387, ``linear_huffman`` :390-411, ``mv_ans`` / ``linear_ans``
+:414-466).  The tensors a weight holds (``rem``, ``exp``, ``offsets`` and the tables) are laid out
+exactly as the reference lays them out, byte for byte.
+
+What is different underneath: a layer is encoded by two CUDA passes over the BF16 weight (size
+pass, prefix sum of the record sizes, emit pass) instead of expanding every symbol to 32
+characters and assembling the format with tensor ops; the per-stream operators the reference
+uses for that are still available (``compress_groups``) and produce the same words.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+from tqdm import tqdm
+
+from . import ops
+from .ans import RANSEncoder
+from .huffman import LUTHuffmanEncoder
+from .utils import get_block_size_n, split_bf16
+
+OP_PER_LANE = 1
+ANS_PRECISION = 8
+SLAB_ROWS = 4096          # rows encoded per slab; 64 padding words follow every slab
+FUSED_MAX_ROWS = 8        # activations with more rows take the decode + GEMM branch
+
+__all__ = [
+    "linear_huffman",
+    "linear_ans",
+    "HuffmanWeight",
+    "ANSWeight",
+    "CompressedLinear",
+    "convert_all_linear",
+    "convert",
+]
+
+
+def _work_device(a: Tensor) -> torch.device:
+    if a.is_cuda:
+        return a.device
+    if not torch.cuda.is_available():
+        raise RuntimeError("bf16_huffman_infer_b200 needs a CUDA device: there is no CPU implementation")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _exp_histogram(a: Tensor) -> Tensor:
+    """256 exponent counts of a BF16 tensor (int64, on the CPU)."""
+    bits = a.contiguous().view(torch.int16).flatten()
+    exp = ((bits >> 7) & 0xFF).to(torch.int64)
+    return torch.bincount(exp, minlength=256).cpu()
+
+
+def _record_offsets(words_per_row: Tensor) -> Tuple[Tensor, int]:
+    """Word offset of every record from the per-record row counts ``[S, M]``.
+
+    Records are stored chunk-major with rows ascending; after every slab of ``SLAB_ROWS`` rows (and
+    after the last, partial slab of a chunk) 64 zero words are inserted, because a Huffman
+    decoder may look one record row past the end of a record (reference ``functional.py:177``,
+    ``:204-231``).
+    """
+    S, M = words_per_row.shape
+    sizes = words_per_row.to(torch.int64) * 64
+    pad = torch.zeros(M, dtype=torch.int64, device=sizes.device)
+    pad[SLAB_ROWS - 1::SLAB_ROWS] = 64
+    pad[M - 1] = 64
+    sizes = (sizes + pad[None, :]).flatten()
+    ends = torch.cumsum(sizes, 0)
+    total = int(ends[-1].item())
+    if total >= 2 ** 31:
+        raise RuntimeError("compressed exponent plane exceeds 2^31 words; split the layer")
+    return (ends - sizes).to(torch.int32).view(S, M), total
+
+
+def mv_huffman(
+    A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor,
+    LUT1: Tensor, LUT2: Tensor, LUT3: Tensor, LUT4: Tensor, code_lengths: Tensor,
+) -> Tensor:
+    """``X @ W.T`` for at most 8 rows of ``X`` from the Huffman-coded ``W`` (reference ``functional.py:28-63``)."""
+    if A_rem.dim() == 2:
+        A_rem = A_rem[None, :, :]
+    if offsets.dim() == 1:
+        offsets = offsets[None, :]
+    split_k, M, N = A_rem.shape
+    X = X.view(-1, split_k, N)
+    assert N % 128 == 0
+    assert X.dtype == torch.bfloat16
+    assert A_rem.device.type == A_exp.device.type == X.device.type == "cuda"
+    assert A_rem.device == A_exp.device == X.device
+    Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
+    ops.gemv_bf16_huffman(
+        A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(),
+        LUT1.contiguous(), LUT2.contiguous(), LUT3.contiguous(), LUT4.contiguous(), code_lengths.contiguous(),
+    )
+    return Y
+
+
+def mv_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, LUT: Tensor) -> Tensor:
+    """``X @ W.T`` for at most 8 rows of ``X`` from the rANS-coded ``W`` (reference ``functional.py:414-444``)."""
+    if A_rem.dim() == 2:
+        A_rem = A_rem[None, :, :]
+    if offsets.dim() == 1:
+        offsets = offsets[None, :]
+    split_k, M, N = A_rem.shape
+    X = X.view(-1, split_k, N)
+    assert N % 128 == 0
+    assert X.dtype == torch.bfloat16
+    assert A_rem.device.type == A_exp.device.type == X.device.type == "cuda"
+    assert A_rem.device == A_exp.device == X.device
+    Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
+    ops.gemv_bf16_ans(A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(), LUT.contiguous())
+    return Y
+
+
+class HuffmanWeight(nn.Module):
+    """A ``[M, K]`` BF16 weight with Huffman-coded exponents.
+
+    Buffers: ``rem`` u8 ``[S, M, K/S]``, ``exp`` i32 ``[words]``, ``offsets`` i32 ``[S, M]``, ``LUT1..LUT4``
+    and ``code_lengths`` u8 ``[256]``.  Passing an instance as the weight of ``F.linear`` dispatches to
+    :func:`linear_huffman`.
+    """
+
+    algo = "huffman"
+
+    def __init__(self, rem: Tensor, exp: Tensor, offsets: Tensor,
+                 LUT1: Tensor, LUT2: Tensor, LUT3: Tensor, LUT4: Tensor, code_lengths: Tensor):
+        super().__init__()
+        self.rem = nn.Buffer(rem)
+        self.exp = nn.Buffer(exp)
+        self.offsets = nn.Buffer(offsets)
+        self.LUT1 = nn.Buffer(LUT1)
+        self.LUT2 = nn.Buffer(LUT2)
+        self.LUT3 = nn.Buffer(LUT3)
+        self.LUT4 = nn.Buffer(LUT4)
+        self.code_lengths = nn.Buffer(code_lengths)
+
+    # -- container protocol ---------------------------------------------------------------
+    def kwargs(self) -> Dict[str, Tensor]:
+        return dict(self.named_buffers())
+
+    @property
+    def shape(self) -> Tuple[int, int]:
+        s, m, n = self.rem.shape
+        return (m, s * n)
+
+    def nbytes(self) -> int:
+        return sum(b.nelement() * b.element_size() for b in self.buffers())
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        if func is not F.linear:
+            return NotImplemented
+        return linear_huffman(*args, **(kwargs or {}))
+
+    def get_weight(self) -> Tensor:
+        """Dense BF16 ``[M, K]`` (reference ``functional.py:99-108``)."""
+        assert self.rem.device.type == "cuda"
+        weight = torch.empty(self.shape, dtype=torch.bfloat16, device=self.rem.device)
+        ops.huffman_decode(self.rem, self.exp, weight, self.offsets,
+                           self.LUT1, self.LUT2, self.LUT3, self.LUT4, self.code_lengths)
+        return weight
+
+    # -- encoding -----------------------------------------------------------------------------
+    @classmethod
+    def get_codec(cls, a: Tensor) -> LUTHuffmanEncoder:
+        """Code tables from the exponent histogram of ``a`` (reference ``functional.py:110-117``)."""
+        codec = LUTHuffmanEncoder()
+        codec.build_lut(_exp_histogram(a.to(_work_device(a))))
+        return codec
+
+    @classmethod
+    def get_lut_kwargs(cls, codec: LUTHuffmanEncoder) -> Dict[str, Tensor]:
+        return {
+            "LUT1": torch.from_numpy(codec.LUT1.copy()),
+            "LUT2": torch.from_numpy(codec.LUT2.copy()),
+            "LUT3": torch.from_numpy(codec.LUT3.copy()),
+            "LUT4": torch.from_numpy(codec.LUT4.copy()),
+            "code_lengths": torch.from_numpy(codec.code_lengths.copy()),
+        }
+
+    @classmethod
+    def compress_groups(cls, x: Tensor, codec: LUTHuffmanEncoder) -> Tuple[Tensor, Tensor]:
+        """Per-stream operator path: ``x`` u8 ``[rows, 64, n]`` -> (words i32 ``[rows*64, n]``, rows' word counts).
+
+        Same result as reference ``functional.py:129-159`` (character expansion by the
+        ``huffman_encode`` operator, then LSB-first packing), kept for operator compatibility and
+        as a cross-check of :meth:`compress_split_n`.
+        """
+        dev = x.device
+        rows, groups, n = x.shape
+        flat = x.reshape(rows * groups, n).contiguous()
+        chars = torch.full((rows * groups, n * 32), ord("0"), dtype=torch.uint8, device=dev)
+        bits = torch.zeros(rows * groups, dtype=torch.int32, device=dev)
+        table = torch.zeros(256, 32, dtype=torch.uint8)
+        for sym, code in codec.huffman_codes.items():
+            path = code[::-1]                      # stored reversed; the stream wants root first
+            table[sym, :len(path)] = torch.tensor([ord(c) for c in path], dtype=torch.uint8)
+        ops.huffman_encode(flat, table.to(dev), chars, bits)
+        nbytes = (bits + 7) // 8
+        row_words = (nbytes.view(rows, groups).amax(dim=1) + 3) // 4
+        weights = (1 << torch.arange(8, device=dev, dtype=torch.int32))
+        packed = ((chars.view(rows * groups, -1, 8).to(torch.int32) - ord("0")) * weights).sum(-1).to(torch.uint8)
+        return packed.view(torch.int32), row_words.to(torch.int32)
+
+    @classmethod
+    def _tables_on(cls, codec, dev) -> Dict[str, Tensor]:
+        return {
+            "code_lengths": torch.from_numpy(codec.code_lengths.copy()).to(dev),
+            "code_values": torch.from_numpy(codec.code_values.view("int32").copy()).to(dev),
+        }
+
+    @classmethod
+    def _encode_layer(cls, w: Tensor, split_k: int, codec) -> Tuple[Tensor, Tensor, Tensor]:
+        """Two-pass device encode of ``w`` (BF16 ``[M, K]`` on a CUDA device)."""
+        dev = w.device
+        M, K = w.shape
+        t = cls._tables_on(codec, dev)
+        rows = torch.empty(split_k, M, dtype=torch.int32, device=dev)
+        ops.huffman_size_pass(w, split_k, t["code_lengths"], rows)
+        offsets, total = _record_offsets(rows)
+        rem = torch.empty(split_k, M, K // split_k, dtype=torch.uint8, device=dev)
+        exp = torch.zeros(total, dtype=torch.int32, device=dev)
+        ops.huffman_emit_pass(w, split_k, t["code_lengths"], t["code_values"], offsets, rem, exp)
+        return rem, exp, offsets
+
+    @classmethod
+    def compress_split_n(cls, a: Tensor, n: int = 2, to_cpu: bool = True):
+        """Encode ``a`` with ``n`` K-chunks (reference ``functional.py:195-238``)."""
+        assert a.dim() == 2 and a.dtype == torch.bfloat16
+        assert a.size(1) % n == 0 and (a.size(1) // n) % 128 == 0, a.shape
+        w = a.detach().to(_work_device(a)).contiguous()
+        codec = cls.get_codec(w)
+        rem, exp, offsets = cls._encode_layer(w, n, codec)
+        if to_cpu:
+            rem, exp, offsets = rem.cpu(), exp.cpu(), offsets.cpu()
+            luts = cls.get_lut_kwargs(codec)
+        else:
+            luts = {k: v.to(w.device) for k, v in cls.get_lut_kwargs(codec).items()}
+        return cls(rem=rem, exp=exp, offsets=offsets, **luts)
+
+    @classmethod
+    def compress(cls, a: Tensor, to_cpu: bool = True):
+        """Encode with the format's own K-chunk choice (reference ``functional.py:240-242``)."""
+        return cls.compress_split_n(a, n=get_block_size_n(a)[0], to_cpu=to_cpu)
+
+
+class ANSWeight(HuffmanWeight):
+    """A ``[M, K]`` BF16 weight with rANS-coded exponents (8-bit probabilities).
+
+    Buffers: ``rem``, ``exp``, ``offsets`` as for :class:`HuffmanWeight`, and ``LUT`` i32 ``[256]`` holding
+    ``sym << 24 | freq << 12 | (slot - cum[sym])`` per slot (reference ``functional.py:245-310``).
+    """
+
+    algo = "ans"
+
+    def __init__(self, rem: Tensor, exp: Tensor, offsets: Tensor, LUT: Tensor):
+        nn.Module.__init__(self)
+        self.rem = nn.Buffer(rem)
+        self.exp = nn.Buffer(exp)
+        self.offsets = nn.Buffer(offsets)
+        self.LUT = nn.Buffer(torch.as_tensor(LUT))
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        if func is not F.linear:
+            return NotImplemented
+        return linear_ans(*args, **(kwargs or {}))
+
+    def get_weight(self) -> Tensor:
+        assert self.rem.device.type == "cuda"
+        weight = torch.empty(self.shape, dtype=torch.bfloat16, device=self.rem.device)
+        ops.ans_decode(self.rem, self.exp, weight, self.offsets, self.LUT)
+        return weight
+
+    @classmethod
+    def get_codec(cls, a: Tensor) -> RANSEncoder:
+        return RANSEncoder(_exp_histogram(a.to(_work_device(a))).tolist(), precision=ANS_PRECISION)
+
+    @classmethod
+    def get_lut_kwargs(cls, codec: RANSEncoder) -> Dict[str, Tensor]:
+        lut = torch.tensor(codec.decode_lut, dtype=torch.int32)
+        return {"LUT": (lut[:, 0] << 24) | (lut[:, 1] << 12) | lut[:, 2]}
+
+    @classmethod
+    def compress_groups(cls, x: Tensor, codec: RANSEncoder) -> Tuple[Tensor, Tensor]:
+        """Per-stream operator path (reference ``functional.py:297-310``): words i32 ``[rows*64, 8n]``, rows' word counts."""
+        dev = x.device
+        rows, groups, n = x.shape
+        flat = x.reshape(rows * groups, n).contiguous()
+        words = torch.zeros(rows * groups, n * 8, dtype=torch.int32, device=dev)
+        counts = torch.zeros(rows * groups, dtype=torch.int32, device=dev)
+        freq = torch.tensor(codec.freq, dtype=torch.int32, device=dev)
+        cum = torch.tensor(codec.cum, dtype=torch.int32, device=dev)
+        ops.ans_encode(flat, freq, cum, words, counts)
+        return words, counts.view(rows, groups).amax(dim=1)
+
+    @classmethod
+    def _encode_layer(cls, w: Tensor, split_k: int, codec) -> Tuple[Tensor, Tensor, Tensor]:
+        dev = w.device
+        M, K = w.shape
+        freq = torch.tensor(codec.freq, dtype=torch.int32, device=dev)
+        cum = torch.tensor(codec.cum, dtype=torch.int32, device=dev)
+        rows = torch.empty(split_k, M, dtype=torch.int32, device=dev)
+        per_stream = torch.empty(split_k, M, 64, dtype=torch.uint8, device=dev)
+        ops.ans_size_pass(w, split_k, freq, cum, rows, per_stream)
+        offsets, total = _record_offsets(rows)
+        rem = torch.empty(split_k, M, K // split_k, dtype=torch.uint8, device=dev)
+        exp = torch.zeros(total, dtype=torch.int32, device=dev)
+        ops.ans_emit_pass(w, split_k, freq, cum, offsets, per_stream, rem, exp)
+        return rem, exp, offsets
+
+
+class CompressedLinear(nn.Module):
+    """``nn.Linear`` replacement whose weight is a :class:`HuffmanWeight` / :class:`ANSWeight` (reference ``functional.py:313-320``)."""
+
+    def __init__(self, weight: HuffmanWeight, bias: Optional[Tensor]) -> None:
+        super().__init__()
+        self.weight = weight
+        self.bias = bias
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1]
+
+    def forward(self, input: Tensor) -> Tensor:
+        return F.linear(input, self.weight, self.bias)
+
+
+def _linear_compressed(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor], fused) -> Tensor:
+    assert input.dim() >= 2, input
+    shape = input.shape
+    input = input.flatten(0, -2)
+    if input.size(0) <= FUSED_MAX_ROWS:
+        output = fused(input)
+        if bias is not None:
+            output += bias[None, :]
+    else:
+        output = F.linear(input, weight.get_weight(), bias)
+    return output.unflatten(0, shape[:-1])
+
+
+def linear_huffman(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor] = None) -> Tensor:
+    """``F.linear`` on a Huffman-coded weight: fused decode+GEMV up to 8 rows, decode then GEMM
+    beyond (reference ``functional.py:390-411``)."""
+    return _linear_compressed(input, weight, bias, lambda x: mv_huffman(
+        weight.rem, weight.exp, x, weight.offsets,
+        weight.LUT1, weight.LUT2, weight.LUT3, weight.LUT4, weight.code_lengths))
+
+
+def linear_ans(input: Tensor, weight: ANSWeight, bias: Optional[Tensor] = None) -> Tensor:
+    """Same for an rANS-coded weight (reference ``functional.py:447-466``)."""
+    return _linear_compressed(input, weight, bias, lambda x: mv_ans(
+        weight.rem, weight.exp, x, weight.offsets, weight.LUT))
+
+
+def _buffers_size(w: nn.Module) -> int:
+    return sum(b.nelement() * b.element_size() for b in w.buffers())
+
+
+def convert(linear: nn.Linear, name, disable_precision_check: bool = True, algo: str = "huffman"):
+    """Compress one ``nn.Linear``; returns a :class:`CompressedLinear`, or ``linear`` itself when
+    compression does not pay (ratio >= 1) or, if checking is enabled, when the fused output is off
+    by 2 % or more on a random input (reference ``functional.py:323-375``).  The module comes back
+    on the device ``linear`` was on."""
+    assert algo in ("huffman", "ans", "smallest")
+    home = linear.weight.device
+    if algo == "huffman":
+        weight = HuffmanWeight.compress(linear.weight)
+    elif algo == "ans":
+        weight = ANSWeight.compress(linear.weight)
+    else:
+        weight = min(
+            [HuffmanWeight.compress(linear.weight), ANSWeight.compress(linear.weight)],
+            key=_buffers_size,
+        )
+    module = CompressedLinear(weight=weight, bias=linear.bias)
+
+    ori_size = linear.weight.nelement() * linear.weight.element_size()
+    ratio = _buffers_size(module.weight) / ori_size
+
+    work = _work_device(linear.weight)
+    linear.to(work)
+    module.to(work)
+    x = torch.randn(1, linear.in_features, dtype=torch.bfloat16, device=work)
+    with torch.no_grad():
+        y1 = linear(x)
+        y2 = module(x)
+    max_rtol = ((y2 - y1).abs() / y1.abs().clamp(min=1e-4)).max().item()
+    linear.to(home)
+    module.to(home)
+
+    fallback = False
+    if ratio >= 1:
+        print(f"\nWarning! {name} ratio = {ratio:.2%}")
+        fallback = True
+    if not disable_precision_check and max_rtol >= 0.02:
+        print(f"\nWarning! {name} output mismatch: max rtol = {max_rtol:.2f}")
+        fallback = True
+    if fallback:
+        print("Fallback to regular nn.Linear")
+        return linear
+    return module
+
+
+def convert_all_linear(model: nn.Module, min_out_features: int = 4096, progress: bool = True,
+                       algo: str = "huffman") -> None:
+    """Replace, in place, every ``nn.Linear`` with at least ``min_out_features`` outputs
+    (reference ``functional.py:378-387``)."""
+    targets = [name for name, mod in model.named_modules()
+               if isinstance(mod, nn.Linear) and mod.out_features >= min_out_features]
+    for name in tqdm(targets, disable=not progress):
+        model.set_submodule(name, convert(model.get_submodule(name), name, algo=algo))

@@ -1,0 +1,121 @@
+/*
+ * C ABI of the B200 (sm_100a) kernels for exponent-coded BF16 linear layers.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless said otherwise.  All
+ * entry points enqueue work on `stream` (a cudaStream_t passed as void*) of the CURRENT CUDA
+ * device and return without synchronising, so they may be called while the stream is being
+ * captured into a CUDA graph.  None of them allocates memory.  Return value: 0 on success, a
+ * BHI_ERR_* code otherwise; bhi_last_error() then returns a message for the calling thread.
+ *
+ * Each entry point replaces one operator of the reference project's torch extension
+ * (lszxb/bf16_huffman_infer; paths below are relative to that project).  The compressed
+ * format is the reference's: see bf16_huffman_infer/functional.py:161-238.
+ *
+ *   A_rem    u8  [split_k, M, Nc]   sign+mantissa bytes, permuted per 128-column block
+ *   A_exp    u32 [exp_words]        entropy-coded exponents, 64 interleaved streams per record
+ *   offsets  i32 [split_k, M]       first word of the record of (chunk, row)
+ *   X        bf16 [batch, split_k*Nc]   activations (row-major)
+ *   Y        bf16 [batch, M]        (gemv)   or   bf16 [M, split_k*Nc]  (decode)
+ *   Nc % 128 == 0, 128 <= Nc <= 16384, 1 <= split_k, 1 <= batch <= 8.
+ */
+#ifndef BF16_HUFFMAN_B200_H_
+#define BF16_HUFFMAN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BHI_OK 0
+#define BHI_ERR_ARG 1      /* a size, pointer or alignment the kernels do not accept */
+#define BHI_ERR_CUDA 2     /* a CUDA runtime call failed (message holds cudaGetErrorString) */
+#define BHI_ERR_LIMIT 3    /* a size beyond a documented fixed limit */
+
+#define BHI_MAX_BATCH 8
+#define BHI_ANS_PRECISION 8
+
+/* Message describing the last error returned on this thread ("" if none). */
+const char *bhi_last_error(void);
+
+/* ABI revision of this library. */
+int bhi_abi_version(void);
+
+/* Which implementation the gemv / decode entry points use:
+ *   0 = automatic (staged fast path when the shape allows it, else the generic path)
+ *   1 = generic path only (one warp per record, direct global loads)
+ * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
+int bhi_set_kernel_path(int path);
+
+/* Y[b, m] = sum_c X[b, c] * W[m, c] computed straight from the Huffman-coded weight.
+ * Replaces torch.ops.bf16_huffman_infer.gemv_bf16_huffman
+ * (bf16_huffman_infer/src/kernel.cu:445-507, schema src/bf16_huffman_infer.cpp:29). */
+int bhi_gemv_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                          const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                          const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                          const uint8_t *LUT4, const uint8_t *code_lengths,
+                          int split_k, int M, int Nc, int batch, void *stream);
+
+/* Dense BF16 weight [M, split_k*Nc] from the Huffman-coded form.
+ * Replaces torch.ops.bf16_huffman_infer.huffman_decode (src/kernel.cu:534-587, schema .cpp:31). */
+int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                       uint16_t *Y, const int32_t *offsets,
+                       const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                       const uint8_t *LUT4, const uint8_t *code_lengths,
+                       int split_k, int M, int Nc, void *stream);
+
+/* Same two operations for the rANS-coded form; LUT is u32[256] with
+ * sym<<24 | freq<<12 | (slot - cum[sym]).
+ * Replace torch.ops.bf16_huffman_infer.gemv_bf16_ans (src/kernel.cu:714-764, schema .cpp:33)
+ * and torch.ops.bf16_huffman_infer.ans_decode (src/kernel.cu:878-919, schema .cpp:35). */
+int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                      int split_k, int M, int Nc, int batch, void *stream);
+int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                   int split_k, int M, int Nc, void *stream);
+
+/* Per-stream Huffman code emission as ASCII '0'/'1' characters.
+ *   data u8 [streams, n]; LUT u8 [256, 32] code strings (root first, NUL padded);
+ *   output u8 [streams, 32*n] (caller pre-fills with '0'); output_lengths i32 [streams] = bits.
+ * Replaces torch.ops.bf16_huffman_infer.huffman_encode (src/kernel.cu:590-644, schema .cpp:30). */
+int bhi_huffman_encode(const uint8_t *data, int streams, int n, const uint8_t *LUT,
+                       uint8_t *output, int32_t *output_lengths, void *stream);
+
+/* Per-stream rANS encode (64-bit state, 32-bit words, symbols taken last to first, words stored
+ * in decode order).  data u8 [streams, n]; freq, cum u32 [256]; output u32 [streams, 8*n];
+ * output_lengths i32 [streams] = words.
+ * Replaces torch.ops.bf16_huffman_infer.ans_encode (src/kernel.cu:767-848, schema .cpp:34). */
+int bhi_ans_encode(const uint8_t *data, int streams, int n, const uint32_t *freq,
+                   const uint32_t *cum, uint32_t *output, int32_t *output_lengths, void *stream);
+
+/* ---- whole-layer encoder -------------------------------------------------------------------
+ * The reference drives the two per-stream operators above from Python and assembles the format
+ * with tensor ops (functional.py:129-238, 297-310), expanding every symbol to 32 characters on
+ * the way.  These entry points produce the same bytes directly from the BF16 weight W [M, K]
+ * (row-major, K = split_k*Nc) in two passes: a size pass and an emit pass, with the record
+ * offsets (a prefix sum with 64 padding words after every 4096 rows) computed in between by the
+ * caller. */
+
+/* Size pass: words_per_row i32 [split_k, M] = words per stream of each record
+ * (functional.py:144-147 for Huffman: ceil(ceil(max bits / 8) / 4); :308 for rANS: max words).
+ * The rANS variant also writes stream_words u8 [split_k, M, 64] for the emit pass. */
+int bhi_huffman_size_pass(const uint16_t *W, int M, int K, int split_k, const uint8_t *code_lengths,
+                          int32_t *words_per_row, void *stream);
+int bhi_ans_size_pass(const uint16_t *W, int M, int K, int split_k, const uint32_t *freq,
+                      const uint32_t *cum, int32_t *words_per_row, uint8_t *stream_words, void *stream);
+
+/* Emit pass: writes A_rem (permuted bytes) and the coded words of every record at its offset.
+ * A_exp must be zero-filled by the caller (padding words are never written).
+ * code_values u32 [256]: code bits with the first path bit in bit 0. */
+int bhi_huffman_emit_pass(const uint16_t *W, int M, int K, int split_k, const uint8_t *code_lengths,
+                          const uint32_t *code_values, const int32_t *offsets,
+                          uint8_t *A_rem, uint32_t *A_exp, void *stream);
+int bhi_ans_emit_pass(const uint16_t *W, int M, int K, int split_k, const uint32_t *freq,
+                      const uint32_t *cum, const int32_t *offsets, const uint8_t *stream_words,
+                      uint8_t *A_rem, uint32_t *A_exp, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BF16_HUFFMAN_B200_H_ */

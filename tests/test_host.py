@@ -1,0 +1,97 @@
+"""Host-side logic of the package that needs no GPU, and the C ABI's export table."""
+import ctypes
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from _util import HEADER, LIB, ROOT, bits_of, header_symbols, make_weight
+
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+import oracle  # noqa: E402
+
+
+def test_library_exports_every_declared_symbol():
+    names = header_symbols()
+    assert len(names) >= 12, names
+    lib = ctypes.CDLL(LIB)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in {HEADER} but not exported"
+    assert lib.bhi_abi_version() >= 1
+
+
+def test_operator_schemas_registered():
+    import bf16_huffman_infer_b200.ops  # noqa: F401
+    ns = torch.ops.bf16_huffman_infer
+    want = {
+        "gemv_bf16_huffman": "(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths) -> ()",
+        "huffman_encode": "(Tensor data, Tensor LUT, Tensor(a!) output, Tensor(b!) output_lengths) -> ()",
+        "huffman_decode": "(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths) -> ()",
+        "gemv_bf16_ans": "(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()",
+        "ans_encode": "(Tensor data, Tensor freq, Tensor cum, Tensor(a!) output, Tensor(b!) output_lengths) -> ()",
+        "ans_decode": "(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()",
+    }
+    for name, sig in want.items():
+        assert str(getattr(ns, name).default._schema) == f"bf16_huffman_infer::{name}{sig}"
+
+
+def test_no_cpu_kernel_is_registered():
+    """Calling an operator with CPU tensors must fail, not fall back."""
+    import bf16_huffman_infer_b200.ops as ops
+    z = torch.zeros(1, 128, 128, dtype=torch.uint8)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ops.ans_decode(z, torch.zeros(64, dtype=torch.int32), torch.zeros(128, 128, dtype=torch.bfloat16),
+                       torch.zeros(1, 128, dtype=torch.int32), torch.zeros(256, dtype=torch.int32))
+
+
+def test_public_names():
+    import bf16_huffman_infer_b200 as pkg
+    for name in ("convert_all_linear", "convert", "HuffmanWeight", "ANSWeight", "CompressedLinear",
+                 "linear_huffman", "get_graphed_model", "get_model_size"):
+        assert hasattr(pkg, name), name
+
+
+def test_split_merge_bf16():
+    from bf16_huffman_infer_b200.utils import merge_bf16, split_bf16
+    w = make_weight(64, 128, 0)
+    w[0, 0] = float("-0.0")
+    w[0, 1] = float("inf")
+    rem, exp = split_bf16(w)
+    orem, oexp = oracle.split(bits_of(w))
+    assert (rem.numpy() == orem).all() and (exp.numpy() == oexp).all()
+    assert torch.equal(merge_bf16(rem, exp).view(torch.int16), w.view(torch.int16))
+
+
+def test_chunk_count_matches_oracle():
+    from bf16_huffman_infer_b200.utils import chunk_count_for_k, get_block_size_n
+    for k in list(range(128, 33000, 128)):
+        try:
+            s = chunk_count_for_k(k)
+        except RuntimeError:
+            s = -1
+        assert s == oracle.chunk_count(k), k
+    assert get_block_size_n(torch.empty(4, 12288)) == (3,)
+    with pytest.raises(RuntimeError):
+        get_block_size_n(torch.empty(4, 100))
+
+
+@pytest.mark.parametrize("S,M", [(1, 128), (3, 5000), (2, 8192), (1, 4096), (2, 4097)])
+def test_record_offsets_match_oracle(S, M):
+    from bf16_huffman_infer_b200.functional import _record_offsets
+    rng = np.random.default_rng(S * 1000 + M)
+    L = rng.integers(1, 20, (S, M)).astype(np.int32)
+    off, total = _record_offsets(torch.from_numpy(L))
+    want = np.zeros((S, M), np.int32)
+    n = oracle.lib().bhi_oracle_layout_offsets(L.ctypes.data_as(ctypes.c_void_p), S, M, want.ctypes.data_as(ctypes.c_void_p))
+    assert total == n and (off.numpy() == want).all()
+
+
+def test_get_model_size_and_shallow_copy():
+    from bf16_huffman_infer_b200.utils import get_model_size, shallow_copy_model
+    m = torch.nn.Sequential(torch.nn.Linear(8, 4), torch.nn.BatchNorm1d(4))
+    size = get_model_size(m)
+    assert size == sum(p.numel() * p.element_size() for p in m.parameters()) + sum(b.numel() * b.element_size() for b in m.buffers())
+    c = shallow_copy_model(m)
+    assert c is not m and c[0] is not m[0] and c[0].weight is m[0].weight
