@@ -54,13 +54,13 @@ static int launch_status(const char *what) {
 }
 
 template <class Codec>
-static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uint16_t *X, uint16_t *Y, int B,
-                    cudaStream_t st) {
+static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                    uint16_t *Y, int B, cudaStream_t st) {
     BHI_REQUIRE(X && Y, "null activation buffer");
     BHI_REQUIRE(B >= 1 && B <= BHI_MAX_BATCH, "batch must be in [1, 8]");
     BHI_REQUIRE(aligned(X, 4) && aligned(Y, 2), "activation buffers must be 4-byte (X) / 2-byte (Y) aligned");
     if (g_path.load() == 0) {
-        int rc = staged_gemv<Codec>(L, targs, X, Y, B, st);
+        int rc = staged_gemv<Codec>(L, targs, prepared, X, Y, B, st);
         if (rc != kStagedDeclined) return rc;
     }
     // one warp per row, enough blocks to give every row its own warp up to 8 waves of blocks per SM
@@ -80,11 +80,12 @@ static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uin
 }
 
 template <class Codec>
-static int run_decode(const Layer &L, const typename Codec::Args &targs, uint16_t *Y, cudaStream_t st) {
+static int run_decode(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, uint16_t *Y,
+                      cudaStream_t st) {
     BHI_REQUIRE(Y, "null output buffer");
     BHI_REQUIRE(aligned(Y, 4), "output must be 4-byte aligned");
     if (g_path.load() == 0) {
-        int rc = staged_decode<Codec>(L, targs, Y, st);
+        int rc = staged_decode<Codec>(L, targs, prepared, Y, st);
         if (rc != kStagedDeclined) return rc;
     }
     const int64_t nrec = static_cast<int64_t>(L.S) * L.M;
@@ -119,6 +120,26 @@ const char *bhi_last_error(void) { return g_error.c_str(); }
 int bhi_abi_version(void) { return 1; }
 int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
 
+int bhi_debug_status(int *status_out) {
+    BHI_REQUIRE(status_out, "null output");
+    int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&v, g_staged_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_staged_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "status read");
+    *status_out = v;
+    return BHI_OK;
+}
+
+#ifdef BHI_TRACE
+// debug builds only: copy the per-warp timeline to the host
+int bhi_debug_trace(long long *out, int count) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * count);
+    return e == cudaSuccess ? BHI_OK : cuda_fail(e, "trace read");
+}
+#endif
+
 int bhi_gemv_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
                           const uint16_t *X, uint16_t *Y, const int32_t *offsets,
                           const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
@@ -128,7 +149,7 @@ int bhi_gemv_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t e
     BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths, "null table");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
     HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
-    return run_gemv<HuffCodec>(L, t, X, Y, batch, static_cast<cudaStream_t>(stream));
+    return run_gemv<HuffCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
@@ -140,7 +161,41 @@ int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_
     BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths, "null table");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
     HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
-    return run_decode<HuffCodec>(L, t, Y, static_cast<cudaStream_t>(stream));
+    return run_decode<HuffCodec>(L, t, nullptr, Y, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_huffman_prepared_bytes(void) { return kPreparedBytes; }
+
+int bhi_huffman_prepare(const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3, const uint8_t *LUT4,
+                        const uint8_t *code_lengths, uint8_t *prepared, void *stream) {
+    BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths && prepared, "null table");
+    BHI_REQUIRE(aligned(prepared, 16), "prepared tables must be 16-byte aligned");
+    HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
+    huffman_prepare_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(t, prepared);
+    return launch_status("huffman_prepare launch");
+}
+
+// A prepared blob carries the exact tables too, so the five table pointers are not needed here.
+int bhi_gemv_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                   const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                   const uint8_t *prepared, int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    const uint8_t *ex = prepared + kLutBytes;
+    HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
+    return run_gemv<HuffCodec>(L, t, prepared, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_huffman_decode_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                uint16_t *Y, const int32_t *offsets, const uint8_t *prepared,
+                                int split_k, int M, int Nc, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    const uint8_t *ex = prepared + kLutBytes;
+    HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
+    return run_decode<HuffCodec>(L, t, prepared, Y, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
@@ -150,7 +205,7 @@ int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_w
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
     AnsArgs t{LUT};
-    return run_gemv<AnsCodec>(L, t, X, Y, batch, static_cast<cudaStream_t>(stream));
+    return run_gemv<AnsCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
@@ -160,7 +215,7 @@ int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_word
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
     AnsArgs t{LUT};
-    return run_decode<AnsCodec>(L, t, Y, static_cast<cudaStream_t>(stream));
+    return run_decode<AnsCodec>(L, t, nullptr, Y, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_huffman_encode(const uint8_t *data, int streams, int n, const uint8_t *LUT,

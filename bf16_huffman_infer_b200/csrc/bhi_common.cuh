@@ -70,9 +70,13 @@ struct HuffArgs {
 };
 
 __device__ __forceinline__ void load_tables(HuffTables &t, const HuffArgs &a, int tid, int nthreads) {
-    const uint8_t *src[5] = {a.lut1, a.lut2, a.lut3, a.lut4, a.len};
-    uint8_t *dst[5] = {t.lut[0], t.lut[1], t.lut[2], t.lut[3], t.len};
-    for (int i = tid; i < 5 * 256; i += nthreads) dst[i >> 8][i & 255] = src[i >> 8][i & 255];
+    for (int i = tid; i < 256; i += nthreads) {
+        t.lut[0][i] = a.lut1[i];
+        t.lut[1][i] = a.lut2[i];
+        t.lut[2][i] = a.lut3[i];
+        t.lut[3][i] = a.lut4[i];
+        t.len[i] = a.len[i];
+    }
 }
 
 __device__ __forceinline__ uint32_t huff_cascade(const HuffTables &t, uint32_t window) {

@@ -1,6 +1,43 @@
-// Staged decode-side kernels (shared-memory ring fed by bulk async copies, pair-symbol decode
-// table).  Placeholder: declines every request so that the generic path runs.
+// Staged decode-side kernels for sm_100a.
+//
+// One persistent CTA per SM, 32 warps (16 for batches above 2, which need more registers).
+//
+// Memory plan.  The exponent record of a (chunk, row) pair is contiguous in global memory; lane 0
+// of the warp that owns the row brings it into the warp's private shared-memory ring with ONE
+// bulk async copy (cp.async.bulk, completion counted on an mbarrier) while the warp is still
+// decoding the previous record.  Stream word w of stream g then sits at ring word 64*w + g, so
+// lane l (streams l and l+32) always reads bank l: the data-dependent word fetches are
+// conflict-free.  The sign/mantissa row needs no reordering between lanes (lane l owns bytes
+// 4l..4l+3 of every 128-byte block), so it is read straight from global memory, 128 bytes per
+// warp and block, four blocks ahead of use and prefetched across record boundaries.  X is staged
+// once per CTA in shared memory, permuted so that one 8-byte load gives a lane its four values of
+// a block.
+//
+// Decode plan (Huffman).  The four byte tables of the format are folded, per CTA, into a
+// 4096-entry table indexed by the next 12 bits of a stream.  An entry yields TWO symbols, already
+// shifted to the exponent positions of a bf16x2 word, and the number of bits they use.  A stream
+// keeps no window registers: its state is one bit cursor; each step re-reads the two ring words
+// under the cursor, so there is no refill branch in the loop.  Windows the 12 bits cannot
+// resolve as a pair give the first symbol only (the second comes from one more lookup) or, for
+// codes longer than 12 bits, fall back to the exact four-table cascade; both are rare.
+//
+// Decode plan (rANS).  One table word per slot, 64-bit state kept as two registers,
+// state' = freq * (state >> 8) + rem as one 32x32+64 multiply-add (a valid stream keeps
+// state < 2^40), refill word fetched from the ring.
+//
+// A warp owns whole output rows (all K-chunks in order): no cross-warp reduction, fixed
+// summation order.  Rows are dealt to CTAs in equal contiguous ranges and to the warps of a CTA
+// through a shared counter.  Records too large for the ring, or whose offsets are not in storage
+// order, are decoded from global memory by the table-exact decoder.
+//
+// Every wait on an mbarrier is bounded; on expiry the warp records a status code in a device
+// word (bhi_debug_status), skips the record and carries on: a lost copy cannot hang the GPU.
+// Cursors are clamped once per group of blocks, so corrupt tables or data cannot walk a read
+// out of the CTA's shared memory.
 #pragma once
+
+#include <mutex>
+#include <type_traits>
 
 #include "bhi_common.cuh"
 
@@ -8,14 +45,602 @@ namespace bhi {
 
 constexpr int kStagedDeclined = -1;
 
+constexpr int kPairBits = 12;
+constexpr int kPairEntries = 1 << kPairBits;
+constexpr int kLutBytes = kPairEntries * 4;    // 16 KB (Huffman pair table; rANS uses the first 1 KB)
+constexpr int kExactBytes = 2048;              // table-exact copies for rare windows / direct records
+constexpr int kCtrlBytes = 1024;               // mbarriers (2 per warp) + row counter
+constexpr int kHeaderBytes = kLutBytes + kExactBytes + kCtrlBytes;
+constexpr int kSlackBytes = 2048;              // readable space above the last ring
+constexpr int kSmemMax = 227 * 1024;
+constexpr int kRingMax = 8192;
+constexpr int kXStageMax = 40 * 1024;          // X is staged in shared memory up to this many bytes
+constexpr int kGroup = 4;                      // blocks per rem prefetch group
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// pair-table entry fields
+constexpr uint32_t kEntSingle = 1u;            // only the first symbol is resolved
+constexpr uint32_t kEntExact = 2u;             // nothing resolved: use the exact tables
+constexpr uint32_t kEntBits8 = 0x78u;          // bits 3..6: stream bits consumed, i.e. 8 * bits in place
+constexpr uint32_t kEntExpMask = 0x7F807F80u;  // the two exponent fields
+
+static_assert(sizeof(HuffTables) <= kExactBytes && sizeof(AnsTables) <= kExactBytes, "exact tables do not fit");
+
+__device__ int g_staged_status = 0;            // 0 = fine; otherwise the last failure code
+
+// Optional per-warp timeline (compile with -DBHI_TRACE): slot i of warp w of CTA c holds the SM
+// clock at trace point i.  Off in normal builds.
+#ifdef BHI_TRACE
+constexpr int kTraceSlots = 8;
+__device__ long long g_trace[160 * 32 * kTraceSlots];
+#define BHI_TRACE_POINT(i)                                                                          \
+    do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 160)                                              \
+        g_trace[(blockIdx.x * 32 + (threadIdx.x >> 5)) * kTraceSlots + (i)] = clock64(); } while (0)
+#else
+#define BHI_TRACE_POINT(i) do {} while (0)
+#endif
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// global -> this CTA's shared memory; both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// packed FP32 fused multiply-add (two lanes per instruction on sm_100)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    uint64_t ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 bf16x2_to_f32x2(uint32_t p) { return make_float2(bf16lo_to_f32(p), bf16hi_to_f32(p)); }
+
+// ---- sinks: what happens to the two bf16x2 words a lane produces per 128-column block --------------
+// gblk = index of the 128-column block inside the full row (chunk * blocks_per_chunk + block).
+template <int B, bool kXS>
+struct GemvSink {
+    float2 acc[B];
+    const uint32_t *x;      // X as bf16 pairs (global)
+    const uint2 *xs;        // X staged in shared memory: [b][gblk][lane] -> {pair at 2l, pair at 64+2l}
+    int64_t row_pairs;      // K / 2
+    int row_blocks;         // K / 128
+    uint16_t *Y;
+    int M;
+
+    __device__ __forceinline__ void stage(uint8_t *x_region, int tid, int nthreads) {
+        if (kXS) {
+            uint2 *dst = reinterpret_cast<uint2 *>(x_region);
+            const int total = B * row_blocks * 32;
+            for (int i = tid; i < total; i += nthreads) {
+                const int l = i & 31, gb = i >> 5;
+                const int b = gb / row_blocks, g = gb - b * row_blocks;
+                const uint32_t *src = x + b * row_pairs + g * 64 + l;
+                dst[i] = make_uint2(__ldg(src), __ldg(src + 32));
+            }
+            xs = dst;
+        }
+    }
+    __device__ __forceinline__ void reset(int lane) {
+        x += lane;
+        xs += lane;
+#pragma unroll
+        for (int b = 0; b < B; b++) acc[b] = make_float2(0.f, 0.f);
+    }
+    __device__ __forceinline__ void begin_record(int) {}
+    __device__ __forceinline__ void put(int gblk, uint32_t w0, uint32_t w1) {
+        const float2 f0 = bf16x2_to_f32x2(w0), f1 = bf16x2_to_f32x2(w1);
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            uint2 xv;
+            if (kXS) {
+                xv = xs[(b * row_blocks + gblk) * 32];
+            } else {
+                const uint32_t *src = x + b * row_pairs + gblk * 64;
+                xv = make_uint2(__ldg(src), __ldg(src + 32));
+            }
+            acc[b] = ffma2(f0, bf16x2_to_f32x2(xv.x), acc[b]);
+            acc[b] = ffma2(f1, bf16x2_to_f32x2(xv.y), acc[b]);
+        }
+    }
+    __device__ __forceinline__ void finish_row(int m, int lane) {
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            const float v = warp_sum(acc[b].x + acc[b].y);
+            if (lane == 0) Y[static_cast<int64_t>(b) * M + m] = f32_to_bf16_rn(v);
+            acc[b] = make_float2(0.f, 0.f);
+        }
+    }
+};
+
+struct DenseSink {
+    uint32_t *out;          // Y as bf16 pairs
+    int64_t row_pairs;      // K / 2
+    uint32_t *row;
+    __device__ __forceinline__ void stage(uint8_t *, int, int) {}
+    __device__ __forceinline__ void reset(int lane) { out += lane; }
+    __device__ __forceinline__ void begin_record(int m) { row = out + static_cast<int64_t>(m) * row_pairs; }
+    __device__ __forceinline__ void put(int gblk, uint32_t w0, uint32_t w1) {
+        row[gblk * 64] = w0;
+        row[gblk * 64 + 32] = w1;
+    }
+    __device__ __forceinline__ void finish_row(int, int) {}
+};
+
+// ---- Huffman: folded pair table ---------------------------------------------------------------------
+// Resolve one symbol from `known` valid low bits of `v` (other bits zero).  Returns its length, 0
+// if the known bits do not determine it.
+__device__ __forceinline__ uint32_t resolve_symbol(const HuffTables &t, uint32_t v, uint32_t known, uint32_t &sym) {
+    sym = t.lut[0][v & 0xFF];
+    if (sym != 255) {
+        const uint32_t n = t.len[sym];
+        return (n >= 1 && n <= 8 && n <= known) ? n : 0;
+    }
+    if (known <= 8) return 0;
+    sym = t.lut[1][(v >> 8) & 0xFF];
+    if (sym == 255) return 0;
+    const uint32_t n = t.len[sym];
+    return (n >= 9 && n <= known) ? n : 0;
+}
+
+// entry: bit0 single, bit1 exact, bits 3..6 bits consumed (x8 in place), bits 7..14 first exponent,
+// bits 16..19 length of the first symbol, bits 23..30 second exponent
+__device__ __forceinline__ void build_pair_table(uint32_t *pair, const HuffTables &t, int tid, int nthreads) {
+    for (int v = tid; v < kPairEntries; v += nthreads) {
+        uint32_t s0, s1, e = kEntExact;
+        const uint32_t l0 = resolve_symbol(t, v, kPairBits, s0);
+        if (l0) {
+            const uint32_t l1 = resolve_symbol(t, static_cast<uint32_t>(v) >> l0, kPairBits - l0, s1);
+            e = l1 ? ((s0 << 7) | (s1 << 23) | (l0 << 16) | ((l0 + l1) << 3))
+                   : ((s0 << 7) | (l0 << 16) | (l0 << 3) | kEntSingle);
+        }
+        pair[v] = e;
+    }
+}
+
+// A stream is a bit cursor: q = 8 * (bit position) + byte offset of the record in shared memory
+// (records start on 256-byte boundaries, so q & ~255 is the byte address of the current word row
+// and (q >> 3) & 31 the bit inside the word).
+struct HuffCursor {
+    uint32_t q;
+    __device__ __forceinline__ uint32_t window(const uint8_t *smem, uint32_t lane_off) const {
+        const uint32_t a = (q & 0xFFFFFF00u) | lane_off;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(smem + a);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t *>(smem + a + 256);
+        return __funnelshift_r(w0, w1, q >> 3);
+    }
+};
+
+// A code longer than the table index: resolve one symbol with the exact four-table cascade.
+// Returns {symbol, length}.  Out of line on purpose: it is rare and must not bloat the loop.
+__device__ __noinline__ uint2 huff_exact_symbol(uint32_t win, const HuffTables *t) {
+    const uint32_t s = huff_cascade(*t, win);
+    return make_uint2(s, t->len[s]);
+}
+
+struct HuffStaged {
+    HuffCursor c0, c1;
+    uint32_t qlim;
+    __device__ __forceinline__ void open(const uint8_t *, uint32_t base, uint32_t limit, int) {
+        c0.q = base;
+        c1.q = base;
+        qlim = limit;
+    }
+    // entry is "exact": take the first symbol from the cascade, leave the entry in "single" form
+    __device__ __forceinline__ void first_exact(uint32_t win, HuffCursor &c, uint32_t &e, const HuffTables &t) {
+        const uint2 f = huff_exact_symbol(win, &t);
+        c.q = min(c.q + 8u * f.y, qlim);
+        e = (f.x << 7) | kEntSingle;
+    }
+    // entry is "single": one more lookup gives the second symbol
+    __device__ __forceinline__ void second(const uint8_t *smem, const uint32_t *fast, const HuffTables &t, uint32_t lane_off,
+                                           HuffCursor &c, uint32_t &e) {
+        const uint32_t win = c.window(smem, lane_off);
+        const uint32_t e2 = fast[win & (kPairEntries - 1)];
+        uint32_t s1 = (e2 >> 7) & 0xFFu, l1 = (e2 >> 16) & 15u;
+        if (e2 & kEntExact) {
+            const uint2 f = huff_exact_symbol(win, &t);
+            s1 = f.x;
+            l1 = f.y;
+        }
+        c.q = min(c.q + 8u * l1, qlim);
+        e = (e & 0x7F80u) | (s1 << 23);
+    }
+    __device__ __forceinline__ void pairs(const uint8_t *smem, const uint32_t *fast, const HuffTables &t, uint32_t lane4,
+                                          uint32_t &e0, uint32_t &e1) {
+        const uint32_t win0 = c0.window(smem, lane4);
+        const uint32_t win1 = c1.window(smem, lane4 + 128);
+        e0 = fast[win0 & (kPairEntries - 1)];
+        e1 = fast[win1 & (kPairEntries - 1)];
+        c0.q += e0 & kEntBits8;
+        c1.q += e1 & kEntBits8;
+        if ((e0 | e1) & (kEntSingle | kEntExact)) {
+            if ((e0 | e1) & kEntExact) {
+                if (e0 & kEntExact) first_exact(win0, c0, e0, t);
+                if (e1 & kEntExact) first_exact(win1, c1, e1, t);
+            }
+            if (e0 & kEntSingle) second(smem, fast, t, lane4, c0, e0);
+            if (e1 & kEntSingle) second(smem, fast, t, lane4 + 128, c1, e1);
+        }
+    }
+    __device__ __forceinline__ void clamp() {
+        c0.q = min(c0.q, qlim);
+        c1.q = min(c1.q, qlim);
+    }
+};
+
+// ---- rANS over the ring ----------------------------------------------------------------------------
+struct AnsLane {
+    uint32_t lo, hi, nx;     // state, byte address of the next word of this stream
+    __device__ __forceinline__ uint32_t symbol(const uint8_t *smem, const uint32_t *slot_table, uint32_t alim) {
+        if (hi == 0 && lo < (1u << kAnsBits)) {
+            hi = lo;
+            lo = *reinterpret_cast<const uint32_t *>(smem + nx);
+            nx = min(nx + 256u, alim);
+        }
+        const uint32_t e = slot_table[lo & kAnsMask];
+        const uint32_t shifted = __funnelshift_r(lo, hi, kAnsBits);      // state >> 8, fits 32 bits
+        const uint64_t next = static_cast<uint64_t>((e >> 12) & 0xFFFu) * shifted + (e & 0xFFFu);
+        lo = static_cast<uint32_t>(next);
+        hi = static_cast<uint32_t>(next >> 32);
+        return e >> 24;
+    }
+};
+
+struct AnsStaged {
+    AnsLane a0, a1;
+    uint32_t alim;
+    __device__ __forceinline__ void open(const uint8_t *smem, uint32_t base, uint32_t limit, int lane) {
+        const uint32_t p = base + 4u * lane;
+        a0.lo = *reinterpret_cast<const uint32_t *>(smem + p);
+        a1.lo = *reinterpret_cast<const uint32_t *>(smem + p + 128);
+        a0.hi = a1.hi = 0;
+        a0.nx = p + 256;
+        a1.nx = p + 128 + 256;
+        alim = limit + 4u * lane;
+    }
+    __device__ __forceinline__ void pairs(const uint8_t *smem, const uint32_t *slot_table, const AnsTables &, uint32_t,
+                                          uint32_t &e0, uint32_t &e1) {
+        const uint32_t s00 = a0.symbol(smem, slot_table, alim);
+        const uint32_t s10 = a1.symbol(smem, slot_table, alim + 128);
+        const uint32_t s01 = a0.symbol(smem, slot_table, alim);
+        const uint32_t s11 = a1.symbol(smem, slot_table, alim + 128);
+        e0 = (s00 << 7) | (s01 << 23);
+        e1 = (s10 << 7) | (s11 << 23);
+    }
+    __device__ __forceinline__ void clamp() {}
+};
+
+template <class Codec> struct StagedOf;
+template <> struct StagedOf<HuffCodec> { using type = HuffStaged; };
+template <> struct StagedOf<AnsCodec> { using type = AnsStaged; };
+
+__device__ __forceinline__ void build_fast_table(uint32_t *fast, const HuffTables &t, int tid, int n) { build_pair_table(fast, t, tid, n); }
+__device__ __forceinline__ void build_fast_table(uint32_t *fast, const AnsTables &t, int tid, int n) {
+    for (int i = tid; i < (1 << kAnsBits); i += n) fast[i] = t.slot[i];
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------
+struct Unit {
+    int m, k;
+    int64_t rec;
+    uint32_t off;          // first exponent word
+    uint32_t exp_bytes;    // staged exponent bytes (0 if the record is read from global memory)
+    uint32_t base;         // byte offset of the record inside dynamic shared memory
+    bool valid, staged;
+};
+
+template <class Codec, class Sink, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink sink_proto, uint32_t x_bytes,
+              uint32_t ring_bytes) {
+    extern __shared__ __align__(256) uint8_t smem[];
+    using Tables = typename Codec::Tables;
+    using Dec = typename StagedOf<Codec>::type;
+
+    uint32_t *fast = reinterpret_cast<uint32_t *>(smem);
+    Tables &tab = *reinterpret_cast<Tables *>(smem + kLutBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kLutBytes + kExactBytes);
+    int *row_counter = reinterpret_cast<int *>(bars + 2 * NW);
+    const uint32_t table_bar = smem_addr(reinterpret_cast<uint8_t *>(row_counter) + 8);   // for the prepared-table copy
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t lane4 = 4u * lane;
+    const uint32_t ring = kHeaderBytes + x_bytes + warp * ring_bytes;     // byte offset in smem, 256-aligned
+    const uint32_t smem_base = smem_addr(smem);
+    const uint32_t bar0 = smem_addr(&bars[2 * warp]);                      // slot s uses the barrier at bar0 + 8*s
+
+    const int row_lo = static_cast<int>(static_cast<int64_t>(L.M) * blockIdx.x / gridDim.x);
+    const int row_hi = static_cast<int>(static_cast<int64_t>(L.M) * (blockIdx.x + 1) / gridDim.x);
+    const int64_t nrec = static_cast<int64_t>(L.S) * L.M;
+    const int nblk = L.Nc >> 7;
+
+    BHI_TRACE_POINT(0);
+    if (threadIdx.x == 0) {
+        *row_counter = 0;
+        mbar_init(table_bar, 1);
+    }
+    if (lane == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (prepared != nullptr && threadIdx.x == 0) {
+        // folded + exact tables were built once for this layer: one bulk copy instead of a rebuild
+        mbar_expect_tx(table_bar, kLutBytes + kExactBytes);
+        bulk_copy_g2s(smem_base, prepared, kLutBytes + kExactBytes, table_bar);
+    }
+
+    auto next_row = [&]() -> int {
+        int v = 0;
+        if (lane == 0) v = atomicAdd(row_counter, 1);
+        return row_lo + __shfl_sync(0xFFFFFFFFu, v, 0);
+    };
+    auto describe = [&](int m, int k, Unit &u) {
+        u.m = m;
+        u.k = k;
+        u.rec = static_cast<int64_t>(k) * L.M + m;
+        u.off = static_cast<uint32_t>(__ldg(L.offsets + u.rec));
+        const int64_t end = (u.rec + 1 < nrec) ? static_cast<int64_t>(static_cast<uint32_t>(__ldg(L.offsets + u.rec + 1)))
+                                               : L.exp_words;
+        const int64_t words = end - static_cast<int64_t>(u.off);
+        u.staged = words > 0 && (words & 63) == 0 && (u.off & 3u) == 0 && end <= L.exp_words &&
+                   words * 4 <= static_cast<int64_t>(ring_bytes);
+        u.exp_bytes = u.staged ? static_cast<uint32_t>(words * 4) : 0u;
+        u.valid = true;
+    };
+    auto issue = [&](Unit &u, int slot) {
+        u.base = slot == 0 ? ring : ring + ring_bytes - u.exp_bytes;
+        if (lane == 0) {
+            const uint32_t bar = bar0 + 8u * slot;
+            mbar_expect_tx(bar, u.exp_bytes);
+            bulk_copy_g2s(smem_base + u.base, L.exp + u.off, u.exp_bytes, bar);
+            prefetch_l2(L.rem + u.rec * L.Nc, static_cast<uint32_t>(L.Nc));
+        }
+    };
+    auto rem_ptr = [&](const Unit &u) { return reinterpret_cast<const uint32_t *>(L.rem + u.rec * L.Nc) + lane; };
+
+    Unit cur, nxt;
+    cur.valid = false;
+    {
+        const int m = next_row();
+        if (m < row_hi) {
+            describe(m, 0, cur);
+            if (cur.staged) issue(cur, 0);
+        }
+    }
+
+    BHI_TRACE_POINT(1);
+    // tables and X: overlaps the first copy in flight
+    Sink sink = sink_proto;
+    sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
+    if (prepared == nullptr) {
+        load_tables(tab, targs, threadIdx.x, blockDim.x);
+        __syncthreads();
+        build_fast_table(fast, tab, threadIdx.x, blockDim.x);
+    } else if (!mbar_wait_bounded(table_bar, 0u)) {
+        if (threadIdx.x == 0) atomicExch(&g_staged_status, 2);
+    }
+    __syncthreads();
+
+    BHI_TRACE_POINT(2);
+    sink.reset(lane);
+    int slot = 0;
+    uint32_t phases = 0u;                          // bit s = parity the next wait on slot s expects
+    uint32_t r_cur[kGroup], r_nxt[kGroup];
+    bool have_first = false;                       // r_cur already holds the first group of `cur`
+
+    while (cur.valid) {
+        nxt.valid = false;
+        if (cur.k + 1 < L.S) {
+            describe(cur.m, cur.k + 1, nxt);
+        } else {
+            const int m = next_row();
+            if (m < row_hi) describe(m, 0, nxt);
+        }
+        const bool early = nxt.valid && nxt.staged && (!cur.staged || cur.exp_bytes + nxt.exp_bytes <= ring_bytes);
+        if (early) issue(nxt, slot ^ 1);
+
+        const int gblk0 = cur.k * nblk;
+        sink.begin_record(cur.m);
+        const uint32_t *rem = rem_ptr(cur);
+        const uint32_t *rem_next = nxt.valid ? rem_ptr(nxt) : rem;
+        bool next_first = false;
+
+        if (cur.staged) {
+            if (!have_first) {
+#pragma unroll
+                for (int j = 0; j < kGroup; j++) r_cur[j] = (j < nblk) ? __ldg(rem + j * 32) : 0u;
+            }
+            const bool arrived = mbar_wait_bounded(bar0 + 8u * slot, (phases >> slot) & 1u);
+            phases ^= 1u << slot;
+            BHI_TRACE_POINT(cur.k == 0 && have_first == false ? 3 : 5);
+            if (arrived) {
+                Dec dec;
+                // cursors may not pass the last word row that is still inside this CTA's shared memory window
+                dec.open(smem, cur.base, cur.base + cur.exp_bytes + 256u, lane);
+                for (int g0 = 0; g0 < nblk; g0 += kGroup) {
+                    const bool last = g0 + kGroup >= nblk;
+#pragma unroll
+                    for (int j = 0; j < kGroup; j++) {
+                        if (!last) r_nxt[j] = (g0 + kGroup + j < nblk) ? __ldg(rem + (g0 + kGroup + j) * 32) : 0u;
+                        else r_nxt[j] = (nxt.valid && j < nblk) ? __ldg(rem_next + j * 32) : 0u;
+                    }
+#pragma unroll
+                    for (int j = 0; j < kGroup; j++) {
+                        if (g0 + j < nblk) {
+                            uint32_t e0, e1;
+                            dec.pairs(smem, fast, tab, lane4, e0, e1);
+                            const uint32_t r = r_cur[j];
+                            sink.put(gblk0 + g0 + j,
+                                     (prmt(r, 0u, 0x1100u) & 0x807F807Fu) | (e0 & kEntExpMask),
+                                     (prmt(r, 0u, 0x3322u) & 0x807F807Fu) | (e1 & kEntExpMask));
+                        }
+                    }
+                    dec.clamp();
+#pragma unroll
+                    for (int j = 0; j < kGroup; j++) r_cur[j] = r_nxt[j];
+                }
+                next_first = nxt.valid;
+            } else if (lane == 0) {
+                atomicExch(&g_staged_status, 1);
+            }
+        } else {
+            // direct record: on-demand global loads with a bounds guard, table-exact decoders
+            typename Codec::template Stream<GlobalWords> s0, s1;
+            s0.init(GlobalWords{L.exp, L.exp_words, static_cast<int64_t>(cur.off) + lane});
+            s1.init(GlobalWords{L.exp, L.exp_words, static_cast<int64_t>(cur.off) + 32 + lane});
+            for (int blk = 0; blk < nblk; blk++) {
+                const uint32_t r = __ldg(rem + blk * 32);
+                const uint32_t a0 = s0.next(tab);
+                const uint32_t b0 = s1.next(tab);
+                const uint32_t a1 = s0.next(tab);
+                const uint32_t b1 = s1.next(tab);
+                sink.put(gblk0 + blk, join_pair<0>(r, (a0 << 7) | (a1 << 23)), join_pair<1>(r, (b0 << 7) | (b1 << 23)));
+            }
+        }
+        BHI_TRACE_POINT(have_first ? 6 : 4);
+        have_first = next_first;
+        if (cur.k == L.S - 1) sink.finish_row(cur.m, lane);
+        __syncwarp();
+        if (nxt.valid && nxt.staged && !early) issue(nxt, slot ^ 1);
+        cur = nxt;
+        slot ^= 1;
+    }
+    BHI_TRACE_POINT(7);
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+template <class K>
+static int staged_prepare(K kernel) {
+    // Opt in to the large dynamic shared-memory carve-out once per device and kernel.
+    static std::mutex mu;
+    static bool done[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BHI_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+        done[dev] = true;
+    }
+    return BHI_OK;
+}
+
+static bool staged_shape_ok(const Layer &L) { return aligned(L.rem, 16) && aligned(L.exp, 16); }
+
+// Layout of a prepared-table blob (Huffman): folded pair table, then the exact tables.
+constexpr int kPreparedBytes = kLutBytes + kExactBytes;
+
+__global__ void __launch_bounds__(1024) huffman_prepare_kernel(HuffArgs targs, uint8_t *blob) {
+    __shared__ HuffTables tab;
+    load_tables(tab, targs, threadIdx.x, blockDim.x);
+    __syncthreads();
+    build_pair_table(reinterpret_cast<uint32_t *>(blob), tab, threadIdx.x, blockDim.x);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(blob + kLutBytes);
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(&tab);
+    for (int i = threadIdx.x; i < kExactBytes / 4; i += blockDim.x)
+        dst[i] = i < static_cast<int>(sizeof(HuffTables) / 4) ? src[i] : 0u;
+}
+
+template <class Codec, class Sink, int NW>
+static int staged_launch(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const Sink &sink,
+                         uint32_t x_bytes, cudaStream_t st) {
+    auto kernel = staged_kernel<Codec, Sink, NW>;
+    if (int rc = staged_prepare(kernel)) return rc;
+    const uint32_t avail = kSmemMax - kHeaderBytes - kSlackBytes - x_bytes;
+    uint32_t ring_bytes = (avail / NW) & ~255u;
+    if (ring_bytes > kRingMax) ring_bytes = kRingMax;
+    const uint32_t smem_bytes = kHeaderBytes + x_bytes + NW * ring_bytes + kSlackBytes;
+    int grid = sm_count();
+    if (grid > L.M) grid = L.M;
+    kernel<<<grid, NW * 32, smem_bytes, st>>>(L, targs, prepared, sink, x_bytes, ring_bytes);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
+}
+
+template <class Codec, int B>
+static int staged_gemv_b(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                         uint16_t *Y, cudaStream_t st) {
+    constexpr int NW = B <= 2 ? 32 : 16;
+    const int64_t K = static_cast<int64_t>(L.S) * L.Nc;
+    const int64_t x_need = ((static_cast<int64_t>(B) * K * 2 + 255) / 256) * 256;
+    if (x_need <= kXStageMax) {
+        GemvSink<B, true> sink{};
+        sink.x = reinterpret_cast<const uint32_t *>(X);
+        sink.row_pairs = K >> 1;
+        sink.row_blocks = static_cast<int>(K >> 7);
+        sink.Y = Y;
+        sink.M = L.M;
+        return staged_launch<Codec, GemvSink<B, true>, NW>(L, targs, prepared, sink, static_cast<uint32_t>(x_need), st);
+    }
+    GemvSink<B, false> sink{};
+    sink.x = reinterpret_cast<const uint32_t *>(X);
+    sink.row_pairs = K >> 1;
+    sink.row_blocks = static_cast<int>(K >> 7);
+    sink.Y = Y;
+    sink.M = L.M;
+    return staged_launch<Codec, GemvSink<B, false>, NW>(L, targs, prepared, sink, 0u, st);
+}
+
 template <class Codec>
-static int staged_gemv(const Layer &, const typename Codec::Args &, const uint16_t *, uint16_t *, int, cudaStream_t) {
+static int staged_gemv(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                       uint16_t *Y, int B, cudaStream_t st) {
+    if (!staged_shape_ok(L) || !aligned(prepared, 16)) return kStagedDeclined;
+    switch (B) {
+        case 1: return staged_gemv_b<Codec, 1>(L, targs, prepared, X, Y, st);
+        case 2: return staged_gemv_b<Codec, 2>(L, targs, prepared, X, Y, st);
+        case 3: return staged_gemv_b<Codec, 3>(L, targs, prepared, X, Y, st);
+        case 4: return staged_gemv_b<Codec, 4>(L, targs, prepared, X, Y, st);
+        case 5: return staged_gemv_b<Codec, 5>(L, targs, prepared, X, Y, st);
+        case 6: return staged_gemv_b<Codec, 6>(L, targs, prepared, X, Y, st);
+        case 7: return staged_gemv_b<Codec, 7>(L, targs, prepared, X, Y, st);
+        case 8: return staged_gemv_b<Codec, 8>(L, targs, prepared, X, Y, st);
+    }
     return kStagedDeclined;
 }
 
 template <class Codec>
-static int staged_decode(const Layer &, const typename Codec::Args &, uint16_t *, cudaStream_t) {
-    return kStagedDeclined;
+static int staged_decode(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, uint16_t *Y,
+                         cudaStream_t st) {
+    if (!staged_shape_ok(L) || !aligned(prepared, 16)) return kStagedDeclined;
+    DenseSink sink{};
+    sink.out = reinterpret_cast<uint32_t *>(Y);
+    sink.row_pairs = (static_cast<int64_t>(L.S) * L.Nc) >> 1;
+    sink.row = nullptr;
+    return staged_launch<Codec, DenseSink, 32>(L, targs, prepared, sink, 0u, st);
 }
 
 }  // namespace bhi

@@ -121,6 +121,55 @@ void boxed_huffman_decode(StableIValue *stack, uint64_t, uint64_t) {
                              ptr<const int32_t>(off), t[0], t[1], t[2], t[3], t[4], v.S, v.M, v.Nc, stream_of(rem)));
 }
 
+// huffman_prepare(LUT1, LUT2, LUT3, LUT4, code_lengths, prepared(a!)) -> ()
+void boxed_huffman_prepare(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor blob = arg(stack, 5);
+    want(blob, ScalarType::Byte, "prepared");
+    STD_TORCH_CHECK(blob.numel() == bhi_huffman_prepared_bytes(), "prepared must have bhi_huffman_prepared_bytes() bytes");
+    const uint8_t *t[5];
+    huff_tables(stack, 0, blob, t);
+    torch::stable::accelerator::DeviceGuard guard(blob.get_device_index());
+    check(bhi_huffman_prepare(t[0], t[1], t[2], t[3], t[4], ptr<uint8_t>(blob), stream_of(blob)));
+}
+
+// gemv_bf16_huffman_prepared(A_rem, A_exp, X, Y(a!), offsets, prepared) -> ()
+void boxed_gemv_bf16_huffman_prepared(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
+           blob = arg(stack, 5);
+    LayerView v = layer_of(rem, exp, off);
+    want(X, ScalarType::BFloat16, "X");
+    want(Y, ScalarType::BFloat16, "Y", 2);
+    want(blob, ScalarType::Byte, "prepared");
+    same_device(rem, X, "X");
+    same_device(rem, Y, "Y");
+    same_device(rem, blob, "prepared");
+    STD_TORCH_CHECK(blob.numel() == bhi_huffman_prepared_bytes(), "prepared has the wrong size");
+    const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
+    STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
+    const int64_t B = X.numel() / K;
+    STD_TORCH_CHECK(B <= BHI_MAX_BATCH, "batch_size <= 8");
+    STD_TORCH_CHECK(Y.numel() == B * v.M, "Y must be [batch, M]");
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_gemv_bf16_huffman_prepared(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words,
+                                         ptr<const uint16_t>(X), ptr<uint16_t>(Y), ptr<const int32_t>(off),
+                                         ptr<const uint8_t>(blob), v.S, v.M, v.Nc, static_cast<int>(B), stream_of(rem)));
+}
+
+// huffman_decode_prepared(A_rem, A_exp, Y(a!), offsets, prepared) -> ()
+void boxed_huffman_decode_prepared(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), Y = arg(stack, 2), off = arg(stack, 3), blob = arg(stack, 4);
+    LayerView v = layer_of(rem, exp, off);
+    want(Y, ScalarType::BFloat16, "Y", 2);
+    want(blob, ScalarType::Byte, "prepared");
+    same_device(rem, Y, "Y");
+    same_device(rem, blob, "prepared");
+    STD_TORCH_CHECK(blob.numel() == bhi_huffman_prepared_bytes(), "prepared has the wrong size");
+    STD_TORCH_CHECK(Y.numel() == static_cast<int64_t>(v.S) * v.M * v.Nc, "Y must be [M, split_k*Nc]");
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_huffman_decode_prepared(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<uint16_t>(Y),
+                                      ptr<const int32_t>(off), ptr<const uint8_t>(blob), v.S, v.M, v.Nc, stream_of(rem)));
+}
+
 // gemv_bf16_ans(A_rem, A_exp, X, Y(a!), offsets, LUT) -> ()
 void boxed_gemv_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
     Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
@@ -293,6 +342,10 @@ STABLE_TORCH_LIBRARY(BHI_TORCH_NAMESPACE, m) {
     m.def("gemv_bf16_ans(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()");
     m.def("ans_encode(Tensor data, Tensor freq, Tensor cum, Tensor(a!) output, Tensor(b!) output_lengths) -> ()");
     m.def("ans_decode(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()");
+    // prepared Huffman tables
+    m.def("huffman_prepare(Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths, Tensor(a!) prepared) -> ()");
+    m.def("gemv_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
+    m.def("huffman_decode_prepared(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     // whole-layer encoder
     m.def("huffman_size_pass(Tensor W, int split_k, Tensor code_lengths, Tensor(a!) words_per_row) -> ()");
     m.def("huffman_emit_pass(Tensor W, int split_k, Tensor code_lengths, Tensor code_values, Tensor offsets, Tensor(a!) rem, Tensor(b!) exp) -> ()");
@@ -307,6 +360,9 @@ STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CUDA, m) {
     m.impl("gemv_bf16_ans", &boxed_gemv_bf16_ans);
     m.impl("ans_encode", &boxed_ans_encode);
     m.impl("ans_decode", &boxed_ans_decode);
+    m.impl("huffman_prepare", &boxed_huffman_prepare);
+    m.impl("gemv_bf16_huffman_prepared", &boxed_gemv_bf16_huffman_prepared);
+    m.impl("huffman_decode_prepared", &boxed_huffman_decode_prepared);
     m.impl("huffman_size_pass", &boxed_huffman_size_pass);
     m.impl("huffman_emit_pass", &boxed_huffman_emit_pass);
     m.impl("ans_size_pass", &boxed_ans_size_pass);

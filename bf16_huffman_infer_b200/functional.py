@@ -100,6 +100,20 @@ def mv_huffman(
     return Y
 
 
+def mv_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, prepared: Tensor) -> Tensor:
+    """:func:`mv_huffman` with the tables already folded (see :meth:`HuffmanWeight.prepared`)."""
+    if A_rem.dim() == 2:
+        A_rem = A_rem[None, :, :]
+    split_k, M, N = A_rem.shape
+    X = X.view(-1, split_k, N)
+    assert N % 128 == 0
+    assert X.dtype == torch.bfloat16
+    assert A_rem.device == A_exp.device == X.device and A_rem.device.type == "cuda"
+    Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
+    ops.gemv_bf16_huffman_prepared(A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(), prepared)
+    return Y
+
+
 def mv_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, LUT: Tensor) -> Tensor:
     """``X @ W.T`` for at most 8 rows of ``X`` from the rANS-coded ``W`` (reference ``functional.py:414-444``)."""
     if A_rem.dim() == 2:
@@ -157,12 +171,23 @@ class HuffmanWeight(nn.Module):
             return NotImplemented
         return linear_huffman(*args, **(kwargs or {}))
 
+    def prepared(self) -> Tensor:
+        """The decode tables folded for the fused kernels (built on first use on each device, so the
+        first call has to happen outside CUDA-graph capture; warm-up iterations take care of that).
+        Not a buffer: it is derived data and stays out of ``state_dict`` and size accounting."""
+        blob = self.__dict__.get("_prepared")
+        if blob is None or blob.device != self.rem.device or self.__dict__.get("_prepared_src") != self.LUT1.data_ptr():
+            blob = torch.empty(ops.PREPARED_BYTES, dtype=torch.uint8, device=self.rem.device)
+            ops.huffman_prepare(self.LUT1, self.LUT2, self.LUT3, self.LUT4, self.code_lengths, blob)
+            self.__dict__["_prepared"] = blob
+            self.__dict__["_prepared_src"] = self.LUT1.data_ptr()
+        return blob
+
     def get_weight(self) -> Tensor:
         """Dense BF16 ``[M, K]`` (reference ``functional.py:99-108``)."""
         assert self.rem.device.type == "cuda"
         weight = torch.empty(self.shape, dtype=torch.bfloat16, device=self.rem.device)
-        ops.huffman_decode(self.rem, self.exp, weight, self.offsets,
-                           self.LUT1, self.LUT2, self.LUT3, self.LUT4, self.code_lengths)
+        ops.huffman_decode_prepared(self.rem, self.exp, weight, self.offsets, self.prepared())
         return weight
 
     # -- encoding -----------------------------------------------------------------------------
@@ -351,9 +376,8 @@ def _linear_compressed(input: Tensor, weight: HuffmanWeight, bias: Optional[Tens
 def linear_huffman(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor] = None) -> Tensor:
     """``F.linear`` on a Huffman-coded weight: fused decode+GEMV up to 8 rows, decode then GEMM
     beyond (reference ``functional.py:390-411``)."""
-    return _linear_compressed(input, weight, bias, lambda x: mv_huffman(
-        weight.rem, weight.exp, x, weight.offsets,
-        weight.LUT1, weight.LUT2, weight.LUT3, weight.LUT4, weight.code_lengths))
+    return _linear_compressed(input, weight, bias, lambda x: mv_huffman_prepared(
+        weight.rem, weight.exp, x, weight.offsets, weight.prepared()))
 
 
 def linear_ans(input: Tensor, weight: ANSWeight, bias: Optional[Tensor] = None) -> Tensor:

@@ -55,6 +55,22 @@ def ans_decode(A_rem: Tensor, A_exp: Tensor, Y: Tensor, offsets: Tensor, LUT: Te
     _ops.ans_decode.default(A_rem, A_exp, Y, offsets, LUT)
 
 
+# ---- prepared Huffman tables (folded once per layer instead of inside every launch) -------------------
+PREPARED_BYTES = 16384 + 2048
+
+
+def huffman_prepare(LUT1: Tensor, LUT2: Tensor, LUT3: Tensor, LUT4: Tensor, code_lengths: Tensor, prepared: Tensor) -> None:
+    _ops.huffman_prepare.default(LUT1, LUT2, LUT3, LUT4, code_lengths, prepared)
+
+
+def gemv_bf16_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
+    _ops.gemv_bf16_huffman_prepared.default(A_rem, A_exp, X, Y, offsets, prepared)
+
+
+def huffman_decode_prepared(A_rem: Tensor, A_exp: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
+    _ops.huffman_decode_prepared.default(A_rem, A_exp, Y, offsets, prepared)
+
+
 # ---- whole-layer encoder passes --------------------------------------------------------------------
 def huffman_size_pass(W: Tensor, split_k: int, code_lengths: Tensor, words_per_row: Tensor) -> None:
     _ops.huffman_size_pass.default(W, split_k, code_lengths, words_per_row)

