@@ -1,0 +1,408 @@
+"""Benchmark of the fused decode+GEMV hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload qwen3-8b|llama3-70b|tiny] [--algo huffman|ans|smallest] [--batch B]
+
+One "step" is one decode token's worth of the hot path: every compressed linear layer of a
+decoder of the named shape applied once, in model order, to a batch of B activation rows (B = 1
+by default).  Weights are synthetic stand-ins for the checkpoints the reference benchmarks
+(N(0, 0.02) BF16, one seed per matrix, generated on the device and checked bit-exact after
+decode); attention, norms and sampling are not part of the path and are not run.
+
+Printed JSON line (rank 0):
+  value    decode tokens/s with activations resident on the device, whole step replayed as one
+           CUDA graph, CUDA-event timed, max over ranks;
+  e2e      the same step through the Python module API with the activations coming from pinned
+           host memory every step and the last layer's output read back to the host;
+  roofline algorithmic compressed bytes per launch / average launch time of the fused kernel,
+           against the measured HBM copy bandwidth of MEASURED_PEAKS.json;
+  cpu_baseline  the CPU restatement of the reference's fused path (oracle/, all host threads) on a
+           bounded sample of the same workload.
+`--impl reference` times that CPU path alone and prints the same line shape.
+With N > 1 (launched under torchrun) every layer is sharded by output rows across the ranks and
+the slices are all-gathered over NCCL (strong scaling: the model is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+WORKLOADS = {
+    # name: (layers, hidden, intermediate, q_heads, kv_heads, head_dim, vocab)
+    "qwen3-8b": (36, 4096, 12288, 32, 8, 128, 151936),
+    "llama3-70b": (80, 8192, 28672, 64, 8, 128, 128256),
+    "tiny": (2, 1024, 3072, 8, 2, 128, 8192),
+}
+# ncu: dram bytes read+written per launch / algorithmic bytes, fused Huffman GEMV, 4096x4096, B=1
+TRAFFIC_OVER_ALGORITHMIC = 1.0014
+
+
+def layer_shapes(name):
+    L, h, inter, qh, kvh, hd, vocab = WORKLOADS[name]
+    per_layer = [("q_proj", qh * hd, h), ("k_proj", kvh * hd, h), ("v_proj", kvh * hd, h), ("o_proj", h, qh * hd),
+                 ("gate_proj", inter, h), ("up_proj", inter, h), ("down_proj", h, inter)]
+    shapes = []
+    for i in range(L):
+        shapes += [(f"layers.{i}.{n}", m, k) for n, m, k in per_layer]
+    shapes.append(("lm_head", vocab, h))
+    return shapes
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---- the CPU arm (oracle): bounded sample of the workload ------------------------------------------------
+def cpu_arm(workload, algo, batch, budget_s=12.0):
+    """Times the CPU restatement of the fused path on the first matrices of the stack, in model order,
+    until about `budget_s` seconds of CPU work have been measured, and scales to a whole step by
+    weight count."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    from bf16_huffman_infer_b200.ans import RANSEncoder
+    from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
+
+    def tables_for_bits(a, bits):
+        hist = oracle.histogram(bits)
+        if a == "huffman":
+            enc = LUTHuffmanEncoder()
+            enc.build_lut(hist)
+            return {"LUT1": enc.LUT1, "LUT2": enc.LUT2, "LUT3": enc.LUT3, "LUT4": enc.LUT4,
+                    "code_lengths": enc.code_lengths, "code_values": enc.code_values}
+        enc = RANSEncoder([int(v) for v in hist], precision=8)
+        lut = np.array([(s << 24) | (f << 12) | r for s, f, r in enc.decode_lut], dtype=np.uint32)
+        return {"freq": np.array(enc.freq, np.uint32), "cum": np.array(enc.cum, np.uint32), "LUT": lut.view(np.int32)}
+
+    shapes = layer_shapes(workload)
+    total_weights = sum(m * k for _, m, k in shapes)
+    timed_weights, seconds, used = 0, 0.0, []
+    for idx, (name, M, K) in enumerate(shapes):
+        g = torch.Generator().manual_seed(idx)
+        W = (torch.randn(M, K, dtype=torch.float32, generator=g) * 0.02).to(torch.bfloat16)
+        Wb = W.view(torch.int16).numpy().view(np.uint16)
+        a = "huffman" if algo == "smallest" else algo
+        tabs = tables_for_bits(a, Wb)
+        rem, exp, offsets, _ = oracle.compress(Wb, a, tabs)
+        x = torch.randn(batch, K, generator=g).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        t0 = time.perf_counter()
+        oracle.gemv(a, rem, exp, offsets, tabs, x)
+        seconds += time.perf_counter() - t0
+        timed_weights += M * K
+        used.append(name)
+        if seconds > budget_s:
+            break
+    step_seconds = seconds * total_weights / timed_weights
+    return {
+        "value": batch / step_seconds, "unit": "tokens/s", "cores": oracle.threads(), "kind": "port",
+        "sample": f"first {len(used)} matrices of the stack ({used[0]} .. {used[-1]}; {timed_weights / 1e6:.0f}M of "
+                  f"{total_weights / 1e6:.0f}M weights), {seconds:.1f} s of CPU time measured, scaled by weight count",
+    }, step_seconds
+
+
+# ---- our arm ------------------------------------------------------------------------------------------
+def build_stack(workload, algo, rank, world, dev, verify=True):
+    """Compress every matrix of the stack on the device; returns modules, shapes and byte counts."""
+    from bf16_huffman_infer_b200 import ANSWeight, CompressedLinear, HuffmanWeight
+    from bf16_huffman_infer_b200.tensor_parallel import RowShardedLinear, shard_rows
+
+    mods, meta = [], []
+    for idx, (name, M, K) in enumerate(layer_shapes(workload)):
+        g = torch.Generator(device=dev).manual_seed(idx)
+        W = (torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        if algo == "huffman":
+            cw = HuffmanWeight.compress(W, to_cpu=False)
+        elif algo == "ans":
+            cw = ANSWeight.compress(W, to_cpu=False)
+        else:
+            cands = [HuffmanWeight.compress(W, to_cpu=False), ANSWeight.compress(W, to_cpu=False)]
+            cw = min(cands, key=lambda w: w.nbytes())
+        if world > 1:
+            assert M % world == 0, f"{name}: {M} rows do not divide across {world} ranks"
+            cw = shard_rows(cw, rank, world)
+        if verify:
+            lo, hi = (M * rank // world, M * (rank + 1) // world)
+            assert torch.equal(cw.get_weight().view(torch.int16), W[lo:hi].view(torch.int16)), f"{name}: decode is not bit-exact"
+        lin = CompressedLinear(cw, None)
+        mod = RowShardedLinear(lin, M) if world > 1 else lin
+        mods.append(mod)
+        meta.append({"name": name, "M": M, "K": K, "local_rows": cw.shape[0], "bytes": cw.nbytes(), "algo": cw.algo})
+        del W
+    return mods, meta
+
+
+def run_step(mods, meta, xs, batch):
+    """One pass over the stack.  Activations follow the model's data flow where shapes allow
+    (o_proj eats q_proj's output, down_proj eats gate_proj's); the rest read the hidden state."""
+    h = xs["hidden"]
+    out = None
+    q = gate = None
+    for mod, info in zip(mods, meta):
+        kind = info["name"].split(".")[-1]
+        if kind == "o_proj":
+            out = mod(q)
+        elif kind == "down_proj":
+            out = mod(gate)
+        else:
+            out = mod(h)
+            if kind == "q_proj":
+                q = out
+            elif kind == "gate_proj":
+                gate = out
+    return out
+
+
+def ours(args, rank, world, dev):
+    import torch.distributed as dist
+
+    t_setup = time.time()
+    mods, meta = build_stack(args.workload, args.algo, rank, world, dev)
+    hidden = WORKLOADS[args.workload][1]
+    B = args.batch
+    g = torch.Generator().manual_seed(12345)
+    x_host = torch.randn(B, hidden, generator=g).to(torch.bfloat16).pin_memory()
+    xs = {"hidden": x_host.to(dev)}
+    torch.cuda.synchronize()
+    setup_s = time.time() - t_setup
+
+    # warm up eagerly (also folds the decode tables), then capture the step as one CUDA graph
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(2):
+            run_step(mods, meta, xs, B)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        y_static = run_step(mods, meta, xs, B)
+    y_host = torch.empty(y_static.shape, dtype=y_static.dtype).pin_memory()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def e2e_step():
+        xs["hidden"].copy_(x_host, non_blocking=True)
+        graph.replay()
+        y_host.copy_(y_static, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    with ClockSampler(dev.index) as clocks:
+        ms = timed(graph.replay, args.steps)
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+
+    ms_step = ms / args.steps
+    launches_per_step = len(mods)
+    alg_bytes = sum(m["bytes"] + B * m["K"] * 2 + B * m["local_rows"] * 2 for m in meta)
+    peak, peak_kind = peaks()
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    total_bytes_all_ranks = alg_bytes * world
+    line = {
+        "metric": "decode tokens/s (hot path: all compressed linear layers of one token)", "value": B / (ms_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights decoded from u8+entropy-coded u8, fp32 accumulate",
+        "data": "synthetic", "impl": "ours",
+        "config": {
+            "workload": f"{args.workload}-shape linear stack ({len(mods)} matrices, {sum(m['M'] * m['K'] for m in meta) / 1e9:.2f}G weights), "
+                        f"batch {B}, algo {args.algo}, rows sharded over {world} GPU(s)",
+            "batch": B, "algo": args.algo, "l2": "inputs larger than L2 (the step streams every compressed weight once)",
+            "compressed_bytes_per_rank": int(sum(m["bytes"] for m in meta)),
+            "ratio": sum(m["bytes"] for m in meta) / (2.0 * sum(m["local_rows"] * m["K"] for m in meta)),
+            "setup_s": round(setup_s, 1),
+        },
+        "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(x_host.numel() * 2),
+                "d2h_bytes_per_step": int(y_host.numel() * 2)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "traffic": alg_bytes / launches_per_step * TRAFFIC_OVER_ALGORITHMIC,
+                     "algorithmic_bytes_per_launch": alg_bytes / launches_per_step,
+                     "avg_launch_us": ms_step * 1e3 / launches_per_step,
+                     "kernel": "staged_kernel<HuffCodec, GemvSink>" if args.algo == "huffman" else "staged_kernel"},
+        "clocks": clocks.summary(),
+    }
+    if world > 1:
+        line["config"]["aggregate_compressed_gbs"] = total_bytes_all_ranks / (ms_step * 1e-3) / 1e9
+    return line, mods, meta, xs
+
+
+def dense_arm(args, dev):
+    """The same stack as plain BF16 nn.Linear layers (torch / cuBLAS), graph-replayed on the same GPU."""
+    shapes = layer_shapes(args.workload)
+    need = sum(m * k for _, m, k in shapes) * 2
+    free, _ = torch.cuda.mem_get_info(dev)
+    if need > free * 0.9:
+        return {"unavailable": f"needs {need / 1e9:.0f} GB, {free / 1e9:.0f} GB free"}
+    mods = []
+    for idx, (name, M, K) in enumerate(shapes):
+        g = torch.Generator(device=dev).manual_seed(idx)
+        lin = torch.nn.Linear(K, M, bias=False, dtype=torch.bfloat16, device=dev)
+        with torch.no_grad():
+            lin.weight.copy_((torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        mods.append(lin)
+    meta = [{"name": n} for n, _, _ in shapes]
+    hidden = WORKLOADS[args.workload][1]
+    xs = {"hidden": torch.randn(args.batch, hidden, device=dev).to(torch.bfloat16)}
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(2):
+            run_step(mods, meta, xs, args.batch)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        run_step(mods, meta, xs, args.batch)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    return {"value": args.batch / (ms_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step, "weight_bytes": need,
+            "gbs": need / (ms_step * 1e-3) / 1e9}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        # the reference's CPU path (restated in oracle/), all host threads, rank 0 only
+        if rank != 0:
+            return
+        per_step = []
+        base = None
+        for _ in range(max(1, min(args.steps, 3))):
+            base, step_seconds = cpu_arm(args.workload, args.algo, args.batch, budget_s=12.0)
+            per_step.append(step_seconds)
+        step_seconds = float(np.median(per_step))
+        base["value"] = args.batch / step_seconds
+        print(json.dumps({
+            "metric": "decode tokens/s (hot path: all compressed linear layers of one token)", "value": base["value"],
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(per_step), "warmup": 0, "ms_per_step": step_seconds * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights, fp32 accumulate",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": f"{args.workload}-shape linear stack, batch {args.batch}, algo {args.algo}", "batch": args.batch, "algo": args.algo},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return
+
+    assert torch.cuda.is_available(), "bench.py --impl ours needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import bf16_huffman_infer_b200  # noqa: F401  (fails loudly if the native libraries are missing)
+
+    line, mods, meta, xs = ours(args, rank, world, dev)
+    del mods, xs
+    torch.cuda.empty_cache()
+    if rank == 0:
+        if world == 1 and not args.no_dense:
+            line["dense_bf16_torch"] = dense_arm(args, dev)
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch)
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
