@@ -49,6 +49,9 @@ TRAFFIC_OVER_ALGORITHMIC = 1.0014
 
 
 def layer_shapes(name):
+    if name.startswith("layer:"):                      # a single matrix, e.g. layer:4096x4096 (for profiler captures)
+        m, k = (int(v) for v in name[6:].split("x"))
+        return [("layers.0.single", m, k)]
     L, h, inter, qh, kvh, hd, vocab = WORKLOADS[name]
     per_layer = [("q_proj", qh * hd, h), ("k_proj", kvh * hd, h), ("v_proj", kvh * hd, h), ("o_proj", h, qh * hd),
                  ("gate_proj", inter, h), ("up_proj", inter, h), ("down_proj", h, inter)]
@@ -210,7 +213,7 @@ def ours(args, rank, world, dev):
 
     t_setup = time.time()
     mods, meta = build_stack(args.workload, args.algo, rank, world, dev)
-    hidden = WORKLOADS[args.workload][1]
+    hidden = meta[0]["K"]
     B = args.batch
     g = torch.Generator().manual_seed(12345)
     x_host = torch.randn(B, hidden, generator=g).to(torch.bfloat16).pin_memory()
@@ -315,7 +318,7 @@ def dense_arm(args, dev):
             lin.weight.copy_((torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16))
         mods.append(lin)
     meta = [{"name": n} for n, _, _ in shapes]
-    hidden = WORKLOADS[args.workload][1]
+    hidden = shapes[0][2]
     xs = {"hidden": torch.randn(args.batch, hidden, device=dev).to(torch.bfloat16)}
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -347,7 +350,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="qwen3-8b", help="one of %s, or layer:MxK for a single matrix" % sorted(WORKLOADS))
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")

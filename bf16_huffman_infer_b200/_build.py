@@ -4,7 +4,7 @@
   (``nvcc`` for sm_100a only; it has no torch or Python dependency);
 * ``_C.abi3.so`` - the PyTorch stable-ABI operator library that forwards to it (host C++ only).
 
-``python -m bf16_huffman_infer_b200._build`` builds both; ``build()`` is also what
+``python bf16_huffman_infer_b200/_build.py`` builds both; ``build()`` is also what
 ``__graft_entry__.build`` calls.
 """
 from __future__ import annotations

@@ -13,6 +13,8 @@ namespace bhi {
 
 static thread_local std::string g_error;
 static std::atomic<int> g_path{0};
+static std::atomic<int> g_overlap{0};
+bool overlap_launches() { return g_overlap.load() != 0; }
 
 void set_error(const std::string &msg) { g_error = msg; }
 int fail(int code, const std::string &msg) {
@@ -119,6 +121,7 @@ extern "C" {
 const char *bhi_last_error(void) { return g_error.c_str(); }
 int bhi_abi_version(void) { return 1; }
 int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
+int bhi_set_launch_overlap(int on) { return g_overlap.exchange(on ? 1 : 0); }
 
 int bhi_debug_status(int *status_out) {
     BHI_REQUIRE(status_out, "null output");

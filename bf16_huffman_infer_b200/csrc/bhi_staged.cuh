@@ -107,6 +107,11 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
 __device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
+// Programmatic dependent launch: let the next kernel in the stream start its weight-only prologue
+// while this one is still running, and wait for the previous kernel's results before touching them.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kSpinLimit; i++)
         if (mbar_try_wait(bar, parity)) return true;
@@ -387,8 +392,13 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     const int nblk = L.Nc >> 7;
 
     BHI_TRACE_POINT(0);
+    pdl_launch_dependents();
+    // The first row of every warp is fixed (row_lo + warp), so its sign/mantissa row can be
+    // requested from HBM before anything else is known; later rows come from the shared counter.
+    if (lane == 0 && row_lo + warp < row_hi)
+        prefetch_l2(L.rem + static_cast<int64_t>(row_lo + warp) * L.Nc, static_cast<uint32_t>(L.Nc));
     if (threadIdx.x == 0) {
-        *row_counter = 0;
+        *row_counter = NW;
         mbar_init(table_bar, 1);
     }
     if (lane == 0) {
@@ -434,17 +444,16 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
 
     Unit cur, nxt;
     cur.valid = false;
-    {
-        const int m = next_row();
-        if (m < row_hi) {
-            describe(m, 0, cur);
-            if (cur.staged) issue(cur, 0);
-        }
+    if (row_lo + warp < row_hi) {
+        describe(row_lo + warp, 0, cur);
+        if (cur.staged) issue(cur, 0);
     }
 
     BHI_TRACE_POINT(1);
     // tables and X: overlaps the first copy in flight
     Sink sink = sink_proto;
+    // Everything above read weights only.  X (and Y) belong to the previous kernel in the stream.
+    pdl_wait();
     sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
     if (prepared == nullptr) {
         load_tables(tab, targs, threadIdx.x, blockDim.x);
@@ -543,6 +552,8 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
 }
 
 // ---- host side -------------------------------------------------------------------------------------
+bool overlap_launches();     // process-wide switch, see bhi_set_launch_overlap
+
 template <class K>
 static int staged_prepare(K kernel) {
     // Opt in to the large dynamic shared-memory carve-out once per device and kernel.
@@ -586,8 +597,17 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
     const uint32_t smem_bytes = kHeaderBytes + x_bytes + NW * ring_bytes + kSlackBytes;
     int grid = sm_count();
     if (grid > L.M) grid = L.M;
-    kernel<<<grid, NW * 32, smem_bytes, st>>>(L, targs, prepared, sink, x_bytes, ring_bytes);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_launches() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
 }
 

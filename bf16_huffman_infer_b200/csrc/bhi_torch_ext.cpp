@@ -247,6 +247,12 @@ void boxed_ans_encode(StableIValue *stack, uint64_t, uint64_t) {
                          stream_of(data)));
 }
 
+// set_launch_overlap(int on) -> int
+void boxed_set_launch_overlap(StableIValue *stack, uint64_t, uint64_t) {
+    const int64_t prev = bhi_set_launch_overlap(static_cast<int>(iarg(stack, 0)));
+    stack[0] = torch::stable::detail::from(prev);
+}
+
 // ---- whole-layer encoder (no counterpart operator in the reference) -------------------------------
 struct EncView {
     int M, K, S;
@@ -346,11 +352,16 @@ STABLE_TORCH_LIBRARY(BHI_TORCH_NAMESPACE, m) {
     m.def("huffman_prepare(Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths, Tensor(a!) prepared) -> ()");
     m.def("gemv_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("huffman_decode_prepared(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
+    m.def("set_launch_overlap(int on) -> int");
     // whole-layer encoder
     m.def("huffman_size_pass(Tensor W, int split_k, Tensor code_lengths, Tensor(a!) words_per_row) -> ()");
     m.def("huffman_emit_pass(Tensor W, int split_k, Tensor code_lengths, Tensor code_values, Tensor offsets, Tensor(a!) rem, Tensor(b!) exp) -> ()");
     m.def("ans_size_pass(Tensor W, int split_k, Tensor freq, Tensor cum, Tensor(a!) words_per_row, Tensor(b!) stream_words) -> ()");
     m.def("ans_emit_pass(Tensor W, int split_k, Tensor freq, Tensor cum, Tensor offsets, Tensor stream_words, Tensor(a!) rem, Tensor(b!) exp) -> ()");
+}
+
+STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CompositeExplicitAutograd, m) {
+    m.impl("set_launch_overlap", &boxed_set_launch_overlap);
 }
 
 STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CUDA, m) {

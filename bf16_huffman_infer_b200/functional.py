@@ -261,6 +261,8 @@ class HuffmanWeight(nn.Module):
         w = a.detach().to(_work_device(a)).contiguous()
         codec = cls.get_codec(w)
         rem, exp, offsets = cls._encode_layer(w, n, codec)
+        # the buffers must be complete in memory before a fused kernel with launch overlap reads them
+        torch.cuda.current_stream(w.device).synchronize()
         if to_cpu:
             rem, exp, offsets = rem.cpu(), exp.cpu(), offsets.cpu()
             luts = cls.get_lut_kwargs(codec)

@@ -19,7 +19,7 @@ try:
 except ImportError as exc:  # pragma: no cover - exercised only on a broken install
     raise ImportError(
         "bf16_huffman_infer_b200: the native libraries are not built "
-        f"({exc}). Run `python -m bf16_huffman_infer_b200._build` (needs nvcc with sm_100a support)."
+        f"({exc}). Run `python bf16_huffman_infer_b200/_build.py` (needs nvcc with sm_100a support)."
     ) from exc
 
 _ops = torch.ops.bf16_huffman_infer
@@ -53,6 +53,13 @@ def ans_encode(data: Tensor, freq: Tensor, cum: Tensor, output: Tensor, output_l
 
 def ans_decode(A_rem: Tensor, A_exp: Tensor, Y: Tensor, offsets: Tensor, LUT: Tensor) -> None:
     _ops.ans_decode.default(A_rem, A_exp, Y, offsets, LUT)
+
+
+def set_launch_overlap(on: bool) -> bool:
+    """Let consecutive fused kernels overlap (programmatic dependent launch).  Safe whenever the
+    weight buffers were not written by a kernel still in flight on the same stream; see
+    ``bhi_set_launch_overlap`` in the C header.  Returns the previous setting."""
+    return bool(_ops.set_launch_overlap.default(int(bool(on))))
 
 
 # ---- prepared Huffman tables (folded once per layer instead of inside every launch) -------------------

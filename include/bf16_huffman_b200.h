@@ -47,6 +47,14 @@ int bhi_abi_version(void);
  * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
 int bhi_set_kernel_path(int path);
 
+/* Launch overlap (programmatic dependent launch), process-wide, off by default.  When on, a fused
+ * kernel may begin while the previous kernel in the stream is still running: it reads the layer's
+ * weight buffers, offsets and tables right away and waits for the previous kernel only before it
+ * touches X and Y.  Turn it on only if the weight buffers are complete in memory before the call
+ * is enqueued (written by an earlier synchronised operation or a memory copy, never by a kernel
+ * still in flight on the same stream).  Returns the previous value. */
+int bhi_set_launch_overlap(int on);
+
 /* Reads and clears the device-side status word of the current device (0 = no incident; 1 = a
  * bounded wait for a bulk copy expired inside a staged kernel and the affected record was
  * skipped).  Synchronises the device; meant for tests and post-mortems, not for the launch path. */
