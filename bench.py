@@ -48,7 +48,26 @@ WORKLOADS = {
 TRAFFIC_OVER_ALGORITHMIC = 1.0014
 
 
+def fuse_shapes(shapes):
+    """Stack q/k/v and gate/up of every block (one launch each), as convert_all_linear(fuse_siblings=True) does."""
+    out, i = [], 0
+    while i < len(shapes):
+        name, m, k = shapes[i]
+        kind = name.split(".")[-1]
+        group = {"q_proj": ("q_proj", "k_proj", "v_proj"), "gate_proj": ("gate_proj", "up_proj")}.get(kind)
+        if group and [s[0].split(".")[-1] for s in shapes[i:i + len(group)]] == list(group):
+            rows = sum(s[1] for s in shapes[i:i + len(group)])
+            out.append((name.rsplit(".", 1)[0] + "." + "+".join(group), rows, k))
+            i += len(group)
+        else:
+            out.append(shapes[i])
+            i += 1
+    return out
+
+
 def layer_shapes(name):
+    if name.endswith("+fused"):
+        return fuse_shapes(layer_shapes(name[:-6]))
     if name.startswith("layer:"):                      # a single matrix, e.g. layer:4096x4096 (for profiler captures)
         m, k = (int(v) for v in name[6:].split("x"))
         return [("layers.0.single", m, k)]
@@ -182,7 +201,14 @@ def build_stack(workload, algo, rank, world, dev, verify=True):
         lin = CompressedLinear(cw, None)
         mod = RowShardedLinear(lin, M) if world > 1 else lin
         mods.append(mod)
-        meta.append({"name": name, "M": M, "K": K, "local_rows": cw.shape[0], "bytes": cw.nbytes(), "algo": cw.algo})
+        info = {"name": name, "M": M, "K": K, "local_rows": cw.shape[0], "bytes": cw.nbytes(), "algo": cw.algo}
+        if "+" in name:                                   # stacked siblings: remember where the first one ends
+            L_, h_, inter_, qh_, kvh_, hd_, _v = WORKLOADS[workload.replace("+fused", "")]
+            if name.endswith("q_proj+k_proj+v_proj"):
+                info["q_rows"] = qh_ * hd_
+            else:
+                info["first_rows"] = inter_
+        meta.append(info)
         del W
     return mods, meta
 
@@ -201,10 +227,10 @@ def run_step(mods, meta, xs, batch):
             out = mod(gate)
         else:
             out = mod(h)
-            if kind == "q_proj":
-                q = out
-            elif kind == "gate_proj":
-                gate = out
+            if kind.startswith("q_proj"):
+                q = out[..., :info["q_rows"]] if "q_rows" in info else out
+            elif kind.startswith("gate_proj"):
+                gate = out[..., :info["first_rows"]] if "first_rows" in info else out
     return out
 
 

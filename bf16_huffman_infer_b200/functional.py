@@ -36,9 +36,14 @@ __all__ = [
     "HuffmanWeight",
     "ANSWeight",
     "CompressedLinear",
+    "FusedCompressedLinear",
     "convert_all_linear",
     "convert",
+    "fuse_sibling_linears",
 ]
+
+# projections that read the same input inside one block of the usual decoder architectures
+SIBLING_GROUPS = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))
 
 
 def _work_device(a: Tensor) -> torch.device:
@@ -437,10 +442,103 @@ def convert(linear: nn.Linear, name, disable_precision_check: bool = True, algo:
     return module
 
 
+class FusedCompressedLinear(nn.Module):
+    """Several ``nn.Linear`` layers that read the same input, stored as ONE compressed weight (their
+    rows concatenated) and computed by ONE fused launch.
+
+    A 1024-row projection cannot fill a B200 on its own (7 rows per SM); stacking q/k/v (or
+    gate/up) gives the kernel enough rows and saves the fixed cost of the extra launches.  The
+    reference attacks the same problem with side streams (``cudastream_utils.py:7-47``).  Each
+    original module is replaced by a :class:`_FusedSlice`; the first one in call order computes the
+    stacked output, the others return their slice of it.
+    """
+
+    def __init__(self, weight: HuffmanWeight, bias: Optional[Tensor], splits):
+        super().__init__()
+        self.weight = weight
+        self.bias = bias
+        self.splits = list(splits)            # [(start, stop), ...] in stacking order
+        self._last_in = None
+        self._last_out = None
+
+    def run(self, input: Tensor) -> Tensor:
+        out = F.linear(input, self.weight, self.bias)
+        self._last_in = (input.data_ptr(), input._version, tuple(input.shape))
+        self._last_out = out
+        return out
+
+    def cached(self, input: Tensor) -> Tensor:
+        key = (input.data_ptr(), input._version, tuple(input.shape))
+        if self._last_out is None or self._last_in != key:
+            return self.run(input)
+        return self._last_out
+
+
+class _FusedSlice(nn.Module):
+    """Stands where one of the stacked layers was; ``leader`` recomputes, the others reuse."""
+
+    def __init__(self, owner: FusedCompressedLinear, index: int, leader: bool):
+        super().__init__()
+        self.__dict__["_owner"] = owner       # not a submodule: the owner is registered once, on the leader
+        if leader:
+            self.fused = owner
+        self.index = index
+        self.leader = leader
+
+    @property
+    def out_features(self) -> int:
+        a, b = self._owner.splits[self.index]
+        return b - a
+
+    def forward(self, input: Tensor) -> Tensor:
+        owner = self._owner
+        out = owner.run(input) if self.leader else owner.cached(input)
+        a, b = owner.splits[self.index]
+        return out[..., a:b]
+
+
+def fuse_sibling_linears(model: nn.Module, groups=SIBLING_GROUPS, algo: str = "huffman", progress: bool = False) -> int:
+    """Stack and compress sibling ``nn.Linear`` layers (same parent, same input width, all with or all
+    without bias) named as in ``groups``.  Call before :func:`convert_all_linear`, which then handles
+    the remaining layers.  Returns the number of groups fused."""
+    todo = []
+    for pname, parent in model.named_modules():
+        for names in groups:
+            mods = [getattr(parent, n, None) for n in names]
+            if not all(isinstance(m, nn.Linear) for m in mods):
+                continue
+            if len({m.in_features for m in mods}) != 1 or len({m.bias is None for m in mods}) != 1:
+                continue
+            todo.append((pname, parent, names, mods))
+    for pname, parent, names, mods in tqdm(todo, disable=not progress):
+        home = mods[0].weight.device
+        stacked = torch.cat([m.weight.detach() for m in mods], dim=0)
+        bias = None if mods[0].bias is None else nn.Parameter(torch.cat([m.bias.detach() for m in mods]), requires_grad=False)
+        if algo == "huffman":
+            weight = HuffmanWeight.compress(stacked)
+        elif algo == "ans":
+            weight = ANSWeight.compress(stacked)
+        else:
+            weight = min([HuffmanWeight.compress(stacked), ANSWeight.compress(stacked)], key=_buffers_size)
+        if _buffers_size(weight) >= stacked.nelement() * stacked.element_size():
+            continue                                      # does not pay: leave the layers alone
+        bounds, at = [], 0
+        for m in mods:
+            bounds.append((at, at + m.out_features))
+            at += m.out_features
+        owner = FusedCompressedLinear(weight, bias, bounds).to(home)
+        for i, n in enumerate(names):
+            setattr(parent, n, _FusedSlice(owner, i, leader=(i == 0)))
+    return len(todo)
+
+
 def convert_all_linear(model: nn.Module, min_out_features: int = 4096, progress: bool = True,
-                       algo: str = "huffman") -> None:
+                       algo: str = "huffman", fuse_siblings: bool = False) -> None:
     """Replace, in place, every ``nn.Linear`` with at least ``min_out_features`` outputs
-    (reference ``functional.py:378-387``)."""
+    (reference ``functional.py:378-387``).  ``fuse_siblings=True`` (not in the reference) first stacks
+    q/k/v and gate/up projections into single compressed weights, see :class:`FusedCompressedLinear`."""
+    if fuse_siblings:
+        fuse_sibling_linears(model, algo=algo, progress=progress)
     targets = [name for name, mod in model.named_modules()
                if isinstance(mod, nn.Linear) and mod.out_features >= min_out_features]
     for name in tqdm(targets, disable=not progress):

@@ -60,3 +60,30 @@ def test_graphed_generate_matches_eager(batch):
     for _ in range(2):                                                # second run reuses the captured graph
         out = graphed.generate(ids.to(DEV), max_new_tokens=12, min_new_tokens=12, do_sample=False).cpu()
         assert torch.equal(out, eager)
+
+
+def test_fused_siblings_give_the_same_tokens():
+    """q/k/v and gate/up stacked into single compressed weights: same logits as the unfused
+    compressed model up to BF16 rounding, graph-capturable, identical greedy tokens eager vs graphed."""
+    from transformers import StaticCache
+    from bf16_huffman_infer_b200 import FusedCompressedLinear, convert_all_linear, get_graphed_model
+
+    cfg, model = _tiny_model(seed=1)
+    ids = torch.randint(0, cfg.vocab_size, (1, 8), generator=torch.Generator().manual_seed(1))
+    model.to(DEV)
+    with torch.no_grad():
+        raw_logits = model(ids.to(DEV)).logits.float().cpu()
+    model.cpu()
+    convert_all_linear(model, min_out_features=256, progress=False, algo="huffman", fuse_siblings=True)
+    fused = [m for m in model.modules() if isinstance(m, FusedCompressedLinear)]
+    assert len(fused) == 2 * cfg.num_hidden_layers
+    assert fused[0].weight.shape[0] == (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    model.to(DEV)
+    with torch.no_grad():
+        logits = model(ids.to(DEV)).logits.float().cpu()
+    assert (logits - raw_logits).abs().max() / raw_logits.pow(2).mean().sqrt() < 0.05
+    cache = StaticCache(config=cfg, max_cache_len=64)
+    eager = _generate(model, cache, ids.to(DEV), 10).cpu()
+    graphed = get_graphed_model(model, cache)
+    out = graphed.generate(ids.to(DEV), max_new_tokens=10, min_new_tokens=10, do_sample=False).cpu()
+    assert torch.equal(out, eager)
