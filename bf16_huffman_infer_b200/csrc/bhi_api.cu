@@ -185,7 +185,7 @@ int bhi_gemv_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, 
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    const uint8_t *ex = prepared + kLutBytes;
+    const uint8_t *ex = prepared + kPairEntries * 4;
     HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
     return run_gemv<HuffCodec>(L, t, prepared, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
@@ -196,7 +196,7 @@ int bhi_huffman_decode_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    const uint8_t *ex = prepared + kLutBytes;
+    const uint8_t *ex = prepared + kPairEntries * 4;
     HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
     return run_decode<HuffCodec>(L, t, prepared, Y, static_cast<cudaStream_t>(stream));
 }

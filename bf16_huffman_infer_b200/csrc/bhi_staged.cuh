@@ -47,22 +47,33 @@ constexpr int kStagedDeclined = -1;
 
 constexpr int kPairBits = 12;
 constexpr int kPairEntries = 1 << kPairBits;
-constexpr int kLutBytes = kPairEntries * 4;    // 16 KB (Huffman pair table; rANS uses the first 1 KB)
+constexpr int kCopies = 4;                     // bank-interleaved copies of the fast table (lane & 3 picks one)
+constexpr int kLutBytes = kPairEntries * 4 * kCopies;   // 64 KB (Huffman pair table; rANS uses the first 4 KB)
 constexpr int kExactBytes = 2048;              // table-exact copies for rare windows / direct records
 constexpr int kCtrlBytes = 1024;               // mbarriers (2 per warp) + row counter
 constexpr int kHeaderBytes = kLutBytes + kExactBytes + kCtrlBytes;
 constexpr int kSlackBytes = 2048;              // readable space above the last ring
 constexpr int kSmemMax = 227 * 1024;
 constexpr int kRingMax = 8192;
-constexpr int kXStageMax = 40 * 1024;          // X is staged in shared memory up to this many bytes
+constexpr int kXStageMax = 32 * 1024;          // X is staged in shared memory up to this many bytes
 constexpr int kGroup = 4;                      // blocks per rem prefetch group
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // pair-table entry fields
-constexpr uint32_t kEntSingle = 1u;            // only the first symbol is resolved
-constexpr uint32_t kEntExact = 2u;             // nothing resolved: use the exact tables
-constexpr uint32_t kEntBits8 = 0x78u;          // bits 3..6: stream bits consumed, i.e. 8 * bits in place
-constexpr uint32_t kEntExpMask = 0x7F807F80u;  // the two exponent fields
+constexpr uint32_t kEntBits = 0xFu;            // bits 0..3: stream bits consumed
+constexpr uint32_t kEntSingle = 0x10u;         // only the first symbol is resolved
+constexpr uint32_t kEntExact = 0x20u;          // nothing resolved: use the exact tables
+constexpr uint32_t kRemMask = 0x807F807Fu;     // sign + mantissa bits of a bf16x2 word; the rest is exponent
+
+// Multipliers handed to the kernel at launch.  Integer multiply-add runs on the FMA pipe, plain
+// shifts/adds on the (half-rate, saturated) integer pipe; because the compiler cannot see these
+// values it has to keep the multiply-add form.
+struct Consts {
+    uint32_t one, eight, sixteen, shift16;
+};
+
+// A prepared-table blob (Huffman): one copy of the folded pair table, then the exact tables.
+constexpr int kPreparedBytes = kPairEntries * 4 + kExactBytes;
 
 static_assert(sizeof(HuffTables) <= kExactBytes && sizeof(AnsTables) <= kExactBytes, "exact tables do not fit");
 
@@ -163,8 +174,10 @@ struct GemvSink {
         for (int b = 0; b < B; b++) acc[b] = make_float2(0.f, 0.f);
     }
     __device__ __forceinline__ void begin_record(int) {}
-    __device__ __forceinline__ void put(int gblk, uint32_t w0, uint32_t w1) {
-        const float2 f0 = bf16x2_to_f32x2(w0), f1 = bf16x2_to_f32x2(w1);
+    __device__ __forceinline__ void put(const Consts &k, int gblk, uint32_t w0, uint32_t w1) {
+        // low half: w << 16 as a multiply (FMA pipe); high half: one mask
+        const float2 f0 = make_float2(__uint_as_float(w0 * k.shift16), bf16hi_to_f32(w0));
+        const float2 f1 = make_float2(__uint_as_float(w1 * k.shift16), bf16hi_to_f32(w1));
 #pragma unroll
         for (int b = 0; b < B; b++) {
             uint2 xv;
@@ -174,8 +187,8 @@ struct GemvSink {
                 const uint32_t *src = x + b * row_pairs + gblk * 64;
                 xv = make_uint2(__ldg(src), __ldg(src + 32));
             }
-            acc[b] = ffma2(f0, bf16x2_to_f32x2(xv.x), acc[b]);
-            acc[b] = ffma2(f1, bf16x2_to_f32x2(xv.y), acc[b]);
+            acc[b] = ffma2(f0, make_float2(__uint_as_float(xv.x * k.shift16), bf16hi_to_f32(xv.x)), acc[b]);
+            acc[b] = ffma2(f1, make_float2(__uint_as_float(xv.y * k.shift16), bf16hi_to_f32(xv.y)), acc[b]);
         }
     }
     __device__ __forceinline__ void finish_row(int m, int lane) {
@@ -195,7 +208,7 @@ struct DenseSink {
     __device__ __forceinline__ void stage(uint8_t *, int, int) {}
     __device__ __forceinline__ void reset(int lane) { out += lane; }
     __device__ __forceinline__ void begin_record(int m) { row = out + static_cast<int64_t>(m) * row_pairs; }
-    __device__ __forceinline__ void put(int gblk, uint32_t w0, uint32_t w1) {
+    __device__ __forceinline__ void put(const Consts &, int gblk, uint32_t w0, uint32_t w1) {
         row[gblk * 64] = w0;
         row[gblk * 64 + 32] = w1;
     }
@@ -203,6 +216,18 @@ struct DenseSink {
 };
 
 // ---- Huffman: folded pair table ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t umad(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// (a & mask) | (b & ~mask) in one logic instruction
+__device__ __forceinline__ uint32_t bitselect(uint32_t a, uint32_t b, uint32_t mask) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(d) : "r"(a), "r"(b), "r"(mask));
+    return d;
+}
+
 // Resolve one symbol from `known` valid low bits of `v` (other bits zero).  Returns its length, 0
 // if the known bits do not determine it.
 __device__ __forceinline__ uint32_t resolve_symbol(const HuffTables &t, uint32_t v, uint32_t known, uint32_t &sym) {
@@ -218,33 +243,27 @@ __device__ __forceinline__ uint32_t resolve_symbol(const HuffTables &t, uint32_t
     return (n >= 9 && n <= known) ? n : 0;
 }
 
-// entry: bit0 single, bit1 exact, bits 3..6 bits consumed (x8 in place), bits 7..14 first exponent,
+// entry: bits 0..3 stream bits consumed, bit 4 single, bit 5 exact, bits 7..14 first exponent,
 // bits 16..19 length of the first symbol, bits 23..30 second exponent
-__device__ __forceinline__ void build_pair_table(uint32_t *pair, const HuffTables &t, int tid, int nthreads) {
-    for (int v = tid; v < kPairEntries; v += nthreads) {
-        uint32_t s0, s1, e = kEntExact;
-        const uint32_t l0 = resolve_symbol(t, v, kPairBits, s0);
-        if (l0) {
-            const uint32_t l1 = resolve_symbol(t, static_cast<uint32_t>(v) >> l0, kPairBits - l0, s1);
-            e = l1 ? ((s0 << 7) | (s1 << 23) | (l0 << 16) | ((l0 + l1) << 3))
-                   : ((s0 << 7) | (l0 << 16) | (l0 << 3) | kEntSingle);
-        }
-        pair[v] = e;
-    }
+__device__ __forceinline__ uint32_t pair_entry(const HuffTables &t, uint32_t v) {
+    uint32_t s0, s1;
+    const uint32_t l0 = resolve_symbol(t, v, kPairBits, s0);
+    if (!l0) return kEntExact;
+    const uint32_t l1 = resolve_symbol(t, v >> l0, kPairBits - l0, s1);
+    return l1 ? ((s0 << 7) | (s1 << 23) | (l0 << 16) | (l0 + l1)) : ((s0 << 7) | (l0 << 16) | l0 | kEntSingle);
 }
 
-// A stream is a bit cursor: q = 8 * (bit position) + byte offset of the record in shared memory
-// (records start on 256-byte boundaries, so q & ~255 is the byte address of the current word row
-// and (q >> 3) & 31 the bit inside the word).
-struct HuffCursor {
-    uint32_t q;
-    __device__ __forceinline__ uint32_t window(const uint8_t *smem, uint32_t lane_off) const {
-        const uint32_t a = (q & 0xFFFFFF00u) | lane_off;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(smem + a);
-        const uint32_t w1 = *reinterpret_cast<const uint32_t *>(smem + a + 256);
-        return __funnelshift_r(w0, w1, q >> 3);
+// Where the kCopies copies of entry v live (word index of copy 0): interleaved, so copy c only ever
+// touches banks congruent to c mod kCopies.  (Picking the bank from the top index bits instead was
+// measured slower: two more integer instructions per lookup cost more than the conflicts they save.)
+__device__ __forceinline__ uint32_t pair_slot(uint32_t v) { return v * kCopies; }
+
+__device__ __forceinline__ void build_pair_table(uint32_t *dst, const HuffTables &t, int tid, int nthreads) {
+    for (int v = tid; v < kPairEntries; v += nthreads) {
+        const uint32_t e = pair_entry(t, v);
+        *reinterpret_cast<uint4 *>(dst + pair_slot(v)) = make_uint4(e, e, e, e);
     }
-};
+}
 
 // A code longer than the table index: resolve one symbol with the exact four-table cascade.
 // Returns {symbol, length}.  Out of line on purpose: it is rare and must not bloat the loop.
@@ -253,67 +272,83 @@ __device__ __noinline__ uint2 huff_exact_symbol(uint32_t win, const HuffTables *
     return make_uint2(s, t->len[s]);
 }
 
+// A stream is a bit cursor p = (bit position) + (byte offset of the record in shared memory) / 8.
+// Records start on 256-byte boundaries, so (p & ~31) * 8 is the byte address of the current word
+// row and p & 31 the bit inside the word.
 struct HuffStaged {
-    HuffCursor c0, c1;
-    uint32_t qlim;
+    uint32_t p0, p1, plim;
     __device__ __forceinline__ void open(const uint8_t *, uint32_t base, uint32_t limit, int) {
-        c0.q = base;
-        c1.q = base;
-        qlim = limit;
+        p0 = p1 = base >> 3;
+        plim = limit >> 3;
     }
-    // entry is "exact": take the first symbol from the cascade, leave the entry in "single" form
-    __device__ __forceinline__ void first_exact(uint32_t win, HuffCursor &c, uint32_t &e, const HuffTables &t) {
-        const uint2 f = huff_exact_symbol(win, &t);
-        c.q = min(c.q + 8u * f.y, qlim);
-        e = (f.x << 7) | kEntSingle;
+    static __device__ __forceinline__ uint32_t window(const uint8_t *smem, const Consts &k, uint32_t p, uint32_t lane_off) {
+        const uint32_t a = umad(p & ~31u, k.eight, lane_off);
+        const uint32_t w0 = *reinterpret_cast<const uint32_t *>(smem + a);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t *>(smem + a + 256);
+        return __funnelshift_r(w0, w1, p);
     }
-    // entry is "single": one more lookup gives the second symbol
-    __device__ __forceinline__ void second(const uint8_t *smem, const uint32_t *fast, const HuffTables &t, uint32_t lane_off,
-                                           HuffCursor &c, uint32_t &e) {
-        const uint32_t win = c.window(smem, lane_off);
-        const uint32_t e2 = fast[win & (kPairEntries - 1)];
+    // this lane's copy of entry (win & 0xFFF): see pair_slot
+    static __device__ __forceinline__ uint32_t lookup(const uint8_t *smem, const Consts &k, uint32_t win, uint32_t copy_off) {
+        return *reinterpret_cast<const uint32_t *>(smem + umad(win & (kPairEntries - 1), k.sixteen, copy_off));
+    }
+    // entry is "single" (or was "exact" and its first symbol has just been taken): one more lookup
+    __device__ __forceinline__ void second(const uint8_t *smem, const Consts &k, const HuffTables &t, uint32_t lane_off,
+                                           uint32_t copy_off, uint32_t &p, uint32_t &e) {
+        const uint32_t win = window(smem, k, p, lane_off);
+        const uint32_t e2 = lookup(smem, k, win, copy_off);
         uint32_t s1 = (e2 >> 7) & 0xFFu, l1 = (e2 >> 16) & 15u;
         if (e2 & kEntExact) {
             const uint2 f = huff_exact_symbol(win, &t);
             s1 = f.x;
             l1 = f.y;
         }
-        c.q = min(c.q + 8u * l1, qlim);
+        p = min(p + l1, plim);
         e = (e & 0x7F80u) | (s1 << 23);
     }
-    __device__ __forceinline__ void pairs(const uint8_t *smem, const uint32_t *fast, const HuffTables &t, uint32_t lane4,
-                                          uint32_t &e0, uint32_t &e1) {
-        const uint32_t win0 = c0.window(smem, lane4);
-        const uint32_t win1 = c1.window(smem, lane4 + 128);
-        e0 = fast[win0 & (kPairEntries - 1)];
-        e1 = fast[win1 & (kPairEntries - 1)];
-        c0.q += e0 & kEntBits8;
-        c1.q += e1 & kEntBits8;
+    __device__ __forceinline__ void first_exact(uint32_t win, const HuffTables &t, uint32_t &p, uint32_t &e) {
+        const uint2 f = huff_exact_symbol(win, &t);
+        p = min(p + f.y, plim);
+        e = (f.x << 7) | kEntSingle;
+    }
+    __device__ __forceinline__ void pairs(const uint8_t *smem, const Consts &k, const HuffTables &t, uint32_t lane4,
+                                          uint32_t copy_off, uint32_t &e0, uint32_t &e1) {
+        const uint32_t win0 = window(smem, k, p0, lane4);
+        const uint32_t win1 = window(smem, k, p1, lane4 + 128);
+        e0 = lookup(smem, k, win0, copy_off);
+        e1 = lookup(smem, k, win1, copy_off);
+        p0 = umad(e0 & kEntBits, k.one, p0);
+        p1 = umad(e1 & kEntBits, k.one, p1);
         if ((e0 | e1) & (kEntSingle | kEntExact)) {
             if ((e0 | e1) & kEntExact) {
-                if (e0 & kEntExact) first_exact(win0, c0, e0, t);
-                if (e1 & kEntExact) first_exact(win1, c1, e1, t);
+                if (e0 & kEntExact) first_exact(win0, t, p0, e0);
+                if (e1 & kEntExact) first_exact(win1, t, p1, e1);
             }
-            if (e0 & kEntSingle) second(smem, fast, t, lane4, c0, e0);
-            if (e1 & kEntSingle) second(smem, fast, t, lane4 + 128, c1, e1);
+            // one pass serves every lane that needs a second symbol on exactly one of its streams
+            const bool on1 = !(e0 & kEntSingle);
+            if ((e0 | e1) & kEntSingle) {
+                uint32_t p = on1 ? p1 : p0, e = on1 ? e1 : e0;
+                second(smem, k, t, on1 ? lane4 + 128 : lane4, copy_off, p, e);
+                if (on1) { p1 = p; e1 = e; } else { p0 = p; e0 = e; }
+            }
+            if (e1 & kEntSingle) second(smem, k, t, lane4 + 128, copy_off, p1, e1);      // both streams needed one
         }
     }
     __device__ __forceinline__ void clamp() {
-        c0.q = min(c0.q, qlim);
-        c1.q = min(c1.q, qlim);
+        p0 = min(p0, plim);
+        p1 = min(p1, plim);
     }
 };
 
 // ---- rANS over the ring ----------------------------------------------------------------------------
 struct AnsLane {
     uint32_t lo, hi, nx;     // state, byte address of the next word of this stream
-    __device__ __forceinline__ uint32_t symbol(const uint8_t *smem, const uint32_t *slot_table, uint32_t alim) {
+    __device__ __forceinline__ uint32_t symbol(const uint8_t *smem, const Consts &k, uint32_t copy_off, uint32_t alim) {
         if (hi == 0 && lo < (1u << kAnsBits)) {
             hi = lo;
             lo = *reinterpret_cast<const uint32_t *>(smem + nx);
             nx = min(nx + 256u, alim);
         }
-        const uint32_t e = slot_table[lo & kAnsMask];
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(smem + umad(lo & kAnsMask, k.sixteen, copy_off));
         const uint32_t shifted = __funnelshift_r(lo, hi, kAnsBits);      // state >> 8, fits 32 bits
         const uint64_t next = static_cast<uint64_t>((e >> 12) & 0xFFFu) * shifted + (e & 0xFFFu);
         lo = static_cast<uint32_t>(next);
@@ -334,12 +369,12 @@ struct AnsStaged {
         a1.nx = p + 128 + 256;
         alim = limit + 4u * lane;
     }
-    __device__ __forceinline__ void pairs(const uint8_t *smem, const uint32_t *slot_table, const AnsTables &, uint32_t,
-                                          uint32_t &e0, uint32_t &e1) {
-        const uint32_t s00 = a0.symbol(smem, slot_table, alim);
-        const uint32_t s10 = a1.symbol(smem, slot_table, alim + 128);
-        const uint32_t s01 = a0.symbol(smem, slot_table, alim);
-        const uint32_t s11 = a1.symbol(smem, slot_table, alim + 128);
+    __device__ __forceinline__ void pairs(const uint8_t *smem, const Consts &k, const AnsTables &, uint32_t,
+                                          uint32_t copy_off, uint32_t &e0, uint32_t &e1) {
+        const uint32_t s00 = a0.symbol(smem, k, copy_off, alim);
+        const uint32_t s10 = a1.symbol(smem, k, copy_off, alim + 128);
+        const uint32_t s01 = a0.symbol(smem, k, copy_off, alim);
+        const uint32_t s11 = a1.symbol(smem, k, copy_off, alim + 128);
         e0 = (s00 << 7) | (s01 << 23);
         e1 = (s10 << 7) | (s11 << 23);
     }
@@ -352,7 +387,10 @@ template <> struct StagedOf<AnsCodec> { using type = AnsStaged; };
 
 __device__ __forceinline__ void build_fast_table(uint32_t *fast, const HuffTables &t, int tid, int n) { build_pair_table(fast, t, tid, n); }
 __device__ __forceinline__ void build_fast_table(uint32_t *fast, const AnsTables &t, int tid, int n) {
-    for (int i = tid; i < (1 << kAnsBits); i += n) fast[i] = t.slot[i];
+    for (int i = tid; i < (1 << kAnsBits); i += n) {
+        const uint32_t e = t.slot[i];
+        *reinterpret_cast<uint4 *>(fast + i * kCopies) = make_uint4(e, e, e, e);
+    }
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
@@ -368,7 +406,7 @@ struct Unit {
 template <class Codec, class Sink, int NW>
 __global__ void __launch_bounds__(NW * 32, 1)
 staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink sink_proto, uint32_t x_bytes,
-              uint32_t ring_bytes) {
+              uint32_t ring_bytes, Consts k) {
     extern __shared__ __align__(256) uint8_t smem[];
     using Tables = typename Codec::Tables;
     using Dec = typename StagedOf<Codec>::type;
@@ -382,6 +420,7 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const uint32_t lane4 = 4u * lane;
+    const uint32_t copy_off = 4u * (lane & (kCopies - 1));            // this lane's copy of the fast table
     const uint32_t ring = kHeaderBytes + x_bytes + warp * ring_bytes;     // byte offset in smem, 256-aligned
     const uint32_t smem_base = smem_addr(smem);
     const uint32_t bar0 = smem_addr(&bars[2 * warp]);                      // slot s uses the barrier at bar0 + 8*s
@@ -408,9 +447,11 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     }
     __syncthreads();
     if (prepared != nullptr && threadIdx.x == 0) {
-        // folded + exact tables were built once for this layer: one bulk copy instead of a rebuild
-        mbar_expect_tx(table_bar, kLutBytes + kExactBytes);
-        bulk_copy_g2s(smem_base, prepared, kLutBytes + kExactBytes, table_bar);
+        // Folded + exact tables were built once for this layer.  The blob holds ONE copy of the folded
+        // table followed by the exact tables; it lands at the tail of the table region (so that the
+        // exact tables fall into their place) and is fanned out into the interleaved copies below.
+        mbar_expect_tx(table_bar, kPreparedBytes);
+        bulk_copy_g2s(smem_base + kLutBytes - kPairEntries * 4, prepared, kPreparedBytes, table_bar);
     }
 
     auto next_row = [&]() -> int {
@@ -459,8 +500,20 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         load_tables(tab, targs, threadIdx.x, blockDim.x);
         __syncthreads();
         build_fast_table(fast, tab, threadIdx.x, blockDim.x);
-    } else if (!mbar_wait_bounded(table_bar, 0u)) {
-        if (threadIdx.x == 0) atomicExch(&g_staged_status, 2);
+    } else {
+        if (!mbar_wait_bounded(table_bar, 0u) && threadIdx.x == 0) atomicExch(&g_staged_status, 2);
+        // fan out: entry v (one word at the tail) -> kCopies words at pair_slot(v).  Slots overlap the raw
+        // copy, so every thread reads all of its raw entries before anybody writes.
+        constexpr int kPer = kPairEntries / (NW * 32);
+        static_assert(kPairEntries % (NW * 32) == 0, "table size must divide by the CTA size");
+        const uint32_t *raw = fast + (kLutBytes - kPairEntries * 4) / 4;
+        uint32_t mine[kPer];
+#pragma unroll
+        for (int i = 0; i < kPer; i++) mine[i] = raw[threadIdx.x + i * NW * 32];
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kPer; i++)
+            *reinterpret_cast<uint4 *>(fast + pair_slot(threadIdx.x + i * NW * 32)) = make_uint4(mine[i], mine[i], mine[i], mine[i]);
     }
     __syncthreads();
 
@@ -507,16 +560,20 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
                         if (!last) r_nxt[j] = (g0 + kGroup + j < nblk) ? __ldg(rem + (g0 + kGroup + j) * 32) : 0u;
                         else r_nxt[j] = (nxt.valid && j < nblk) ? __ldg(rem_next + j * 32) : 0u;
                     }
+                    auto step = [&](int j) {
+                        uint32_t e0, e1;
+                        dec.pairs(smem, k, tab, lane4, copy_off, e0, e1);
+                        const uint32_t r = r_cur[j];
+                        sink.put(k, gblk0 + g0 + j, bitselect(prmt(r, 0u, 0x1100u), e0, kRemMask),
+                                 bitselect(prmt(r, 0u, 0x3322u), e1, kRemMask));
+                    };
+                    if (g0 + kGroup <= nblk) {
 #pragma unroll
-                    for (int j = 0; j < kGroup; j++) {
-                        if (g0 + j < nblk) {
-                            uint32_t e0, e1;
-                            dec.pairs(smem, fast, tab, lane4, e0, e1);
-                            const uint32_t r = r_cur[j];
-                            sink.put(gblk0 + g0 + j,
-                                     (prmt(r, 0u, 0x1100u) & 0x807F807Fu) | (e0 & kEntExpMask),
-                                     (prmt(r, 0u, 0x3322u) & 0x807F807Fu) | (e1 & kEntExpMask));
-                        }
+                        for (int j = 0; j < kGroup; j++) step(j);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kGroup; j++)
+                            if (g0 + j < nblk) step(j);
                     }
                     dec.clamp();
 #pragma unroll
@@ -537,7 +594,7 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
                 const uint32_t b0 = s1.next(tab);
                 const uint32_t a1 = s0.next(tab);
                 const uint32_t b1 = s1.next(tab);
-                sink.put(gblk0 + blk, join_pair<0>(r, (a0 << 7) | (a1 << 23)), join_pair<1>(r, (b0 << 7) | (b1 << 23)));
+                sink.put(k, gblk0 + blk, join_pair<0>(r, (a0 << 7) | (a1 << 23)), join_pair<1>(r, (b0 << 7) | (b1 << 23)));
             }
         }
         BHI_TRACE_POINT(have_first ? 6 : 4);
@@ -572,15 +629,13 @@ static int staged_prepare(K kernel) {
 
 static bool staged_shape_ok(const Layer &L) { return aligned(L.rem, 16) && aligned(L.exp, 16); }
 
-// Layout of a prepared-table blob (Huffman): folded pair table, then the exact tables.
-constexpr int kPreparedBytes = kLutBytes + kExactBytes;
 
 __global__ void __launch_bounds__(1024) huffman_prepare_kernel(HuffArgs targs, uint8_t *blob) {
     __shared__ HuffTables tab;
     load_tables(tab, targs, threadIdx.x, blockDim.x);
     __syncthreads();
-    build_pair_table(reinterpret_cast<uint32_t *>(blob), tab, threadIdx.x, blockDim.x);
-    uint32_t *dst = reinterpret_cast<uint32_t *>(blob + kLutBytes);
+    for (int v = threadIdx.x; v < kPairEntries; v += blockDim.x) reinterpret_cast<uint32_t *>(blob)[v] = pair_entry(tab, v);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(blob + kPairEntries * 4);
     const uint32_t *src = reinterpret_cast<const uint32_t *>(&tab);
     for (int i = threadIdx.x; i < kExactBytes / 4; i += blockDim.x)
         dst[i] = i < static_cast<int>(sizeof(HuffTables) / 4) ? src[i] : 0u;
@@ -607,7 +662,8 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes);
+    const Consts k{1u, 8u, 16u, 65536u};
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes, k);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
 }
 

@@ -79,7 +79,7 @@ int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_
 
 /* ---- prepared Huffman tables ---------------------------------------------------------------
  * The fused kernels do not decode with the four byte tables directly: they fold them into a
- * 4096-entry two-symbols-per-lookup table.  The two entry points above rebuild that table inside
+ * 4096-entry two-symbols-per-lookup table (kept in four bank-interleaved copies).  The two entry points above rebuild that table inside
  * every launch, which costs a few microseconds per call.  A caller that keeps a layer around can
  * fold the tables once into a blob of bhi_huffman_prepared_bytes() bytes (16-byte aligned device
  * memory owned by the caller) and pass the blob instead of the five tables; the kernels then
