@@ -376,7 +376,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qwen3-8b", help="one of %s, or layer:MxK for a single matrix" % sorted(WORKLOADS))
+    ap.add_argument("--workload", default="qwen3-8b+fused",
+                    help="one of %s, optionally with +fused (q/k/v and gate/up stacked into one launch each), "
+                         "or layer:MxK for a single matrix" % sorted(WORKLOADS))
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")

@@ -9,7 +9,7 @@
 // lane l (streams l and l+32) always reads bank l: the data-dependent word fetches are
 // conflict-free.  The sign/mantissa row needs no reordering between lanes (lane l owns bytes
 // 4l..4l+3 of every 128-byte block), so it is read straight from global memory, 128 bytes per
-// warp and block, four blocks ahead of use and prefetched across record boundaries.  X is staged
+// warp and block, eight blocks ahead of use and prefetched across record boundaries.  X is staged
 // once per CTA in shared memory, permuted so that one 8-byte load gives a lane its four values of
 // a block.
 //
@@ -56,7 +56,7 @@ constexpr int kSlackBytes = 2048;              // readable space above the last 
 constexpr int kSmemMax = 227 * 1024;
 constexpr int kRingMax = 8192;
 constexpr int kXStageMax = 32 * 1024;          // X is staged in shared memory up to this many bytes
-constexpr int kGroup = 4;                      // blocks per rem prefetch group
+constexpr int kGroup = 8;                      // blocks per rem prefetch group (8 measured 2 % faster than 4)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // pair-table entry fields
