@@ -331,7 +331,7 @@ def ours(args, rank, world, dev):
 
 def dense_arm(args, dev):
     """The same stack as plain BF16 nn.Linear layers (torch / cuBLAS), graph-replayed on the same GPU."""
-    shapes = layer_shapes(args.workload)
+    shapes = layer_shapes(args.workload.replace("+fused", ""))      # an uncompressed model keeps its projections separate
     need = sum(m * k for _, m, k in shapes) * 2
     free, _ = torch.cuda.mem_get_info(dev)
     if need > free * 0.9:
