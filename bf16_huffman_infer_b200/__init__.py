@@ -10,6 +10,7 @@ from .functional import *  # noqa: F401,F403
 from .functional import mv_ans, mv_huffman  # noqa: F401
 from .cudagraph_utils import get_graphed_model  # noqa: F401
 from .utils import get_model_size  # noqa: F401
+from .checkpoint import load_compressed, save_compressed  # noqa: F401
 
 import os as _os
 from . import ops as _ops_mod

@@ -95,3 +95,46 @@ def test_get_model_size_and_shallow_copy():
     assert size == sum(p.numel() * p.element_size() for p in m.parameters()) + sum(b.numel() * b.element_size() for b in m.buffers())
     c = shallow_copy_model(m)
     assert c is not m and c[0] is not m[0] and c[0].weight is m[0].weight
+
+
+def test_compressed_checkpoint_roundtrip(tmp_path):
+    """save_compressed / load_compressed rebuild the compressed modules (plain and stacked) on the CPU."""
+    import numpy as np
+    from _util import tables_for
+    from bf16_huffman_infer_b200 import CompressedLinear, HuffmanWeight, ANSWeight, load_compressed, save_compressed
+    from bf16_huffman_infer_b200.functional import FusedCompressedLinear, _FusedSlice
+
+    def compressed(algo, M, K, seed):
+        W = make_weight(M, K, seed)
+        Wb = bits_of(W)
+        tabs = tables_for(algo, oracle.histogram(Wb))
+        rem, exp, offsets, _ = oracle.compress(Wb, algo, tabs)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+        if algo == "huffman":
+            return HuffmanWeight(t(rem), t(exp), t(offsets), *[t(tabs[k]) for k in ("LUT1", "LUT2", "LUT3", "LUT4", "code_lengths")])
+        return ANSWeight(t(rem), t(exp), t(offsets), t(tabs["LUT"]))
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = torch.nn.Linear(512, 256, bias=True)
+            self.k_proj = torch.nn.Linear(512, 128, bias=True)
+            self.o_proj = torch.nn.Linear(512, 512, bias=False)
+            self.norm = torch.nn.LayerNorm(512)
+
+    src = Block().to(torch.bfloat16)
+    owner = FusedCompressedLinear(compressed("huffman", 384, 512, 1), torch.nn.Parameter(torch.randn(384).to(torch.bfloat16)), [(0, 256), (256, 384)])
+    src.q_proj = _FusedSlice(owner, 0, True)
+    src.k_proj = _FusedSlice(owner, 1, False)
+    src.o_proj = CompressedLinear(compressed("ans", 512, 512, 2), None)
+    path = str(tmp_path / "model.pt")
+    save_compressed(src, path)
+
+    dst = load_compressed(Block().to(torch.bfloat16), path)
+    assert isinstance(dst.o_proj, CompressedLinear) and isinstance(dst.o_proj.weight, ANSWeight)
+    assert isinstance(dst.q_proj, _FusedSlice) and dst.q_proj.leader and not dst.k_proj.leader
+    assert dst.k_proj._owner is dst.q_proj._owner and dst.q_proj._owner.splits == [(0, 256), (256, 384)]
+    a, b = src.state_dict(), dst.state_dict()
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
