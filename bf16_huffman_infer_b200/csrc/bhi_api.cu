@@ -8,6 +8,7 @@
 #include "bhi_encode.cuh"
 #include "bhi_generic.cuh"
 #include "bhi_staged.cuh"
+#include "bhi_gemm.cuh"
 
 namespace bhi {
 
@@ -97,6 +98,16 @@ static int run_decode(const Layer &L, const typename Codec::Args &targs, const u
     if (blocks > cap) blocks = cap;
     decode_generic_kernel<Codec><<<static_cast<int>(blocks), kGenericThreads, 0, st>>>(L, targs, Y);
     return launch_status("decode launch");
+}
+
+template <class Codec>
+static int run_linear(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                      uint16_t *Y, int B, cudaStream_t st) {
+    BHI_REQUIRE(X && Y, "null activation buffer");
+    BHI_REQUIRE(B >= 1 && B <= BHI_MAX_LINEAR_BATCH, "batch must be in [1, 128]");
+    BHI_REQUIRE(aligned(X, 16) && aligned(Y, 2), "activation buffers must be 16-byte (X) / 2-byte (Y) aligned");
+    BHI_REQUIRE(aligned(L.rem, 16) && aligned(L.exp, 16) && aligned(prepared, 16), "weight buffers must be 16-byte aligned");
+    return gemm_launch<Codec>(L, targs, prepared, X, Y, B, st);
 }
 
 static int check_enc(const void *W, int M, int K, int S) {
@@ -199,6 +210,39 @@ int bhi_huffman_decode_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int
     const uint8_t *ex = prepared + kPairEntries * 4;
     HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
     return run_decode<HuffCodec>(L, t, prepared, Y, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_linear_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                            const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                            const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                            const uint8_t *LUT4, const uint8_t *code_lengths,
+                            int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths, "null table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
+    return run_linear<HuffCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_linear_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                     const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                     const uint8_t *prepared, int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    const uint8_t *ex = prepared + kPairEntries * 4;
+    HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
+    return run_linear<HuffCodec>(L, t, prepared, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                        int split_k, int M, int Nc, int batch, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    AnsArgs t{LUT};
+    return run_linear<AnsCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,

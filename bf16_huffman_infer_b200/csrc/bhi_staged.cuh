@@ -69,7 +69,7 @@ constexpr uint32_t kRemMask = 0x807F807Fu;     // sign + mantissa bits of a bf16
 // shifts/adds on the (half-rate, saturated) integer pipe; because the compiler cannot see these
 // values it has to keep the multiply-add form.
 struct Consts {
-    uint32_t one, eight, sixteen, shift16;
+    uint32_t one, eight, entry, shift16;     // entry = bytes between consecutive fast-table entries (4 * copies)
 };
 
 // A prepared-table blob (Huffman): one copy of the folded pair table, then the exact tables.
@@ -289,7 +289,7 @@ struct HuffStaged {
     }
     // this lane's copy of entry (win & 0xFFF): see pair_slot
     static __device__ __forceinline__ uint32_t lookup(const uint8_t *smem, const Consts &k, uint32_t win, uint32_t copy_off) {
-        return *reinterpret_cast<const uint32_t *>(smem + umad(win & (kPairEntries - 1), k.sixteen, copy_off));
+        return *reinterpret_cast<const uint32_t *>(smem + umad(win & (kPairEntries - 1), k.entry, copy_off));
     }
     // entry is "single" (or was "exact" and its first symbol has just been taken): one more lookup
     __device__ __forceinline__ void second(const uint8_t *smem, const Consts &k, const HuffTables &t, uint32_t lane_off,
@@ -348,7 +348,7 @@ struct AnsLane {
             lo = *reinterpret_cast<const uint32_t *>(smem + nx);
             nx = min(nx + 256u, alim);
         }
-        const uint32_t e = *reinterpret_cast<const uint32_t *>(smem + umad(lo & kAnsMask, k.sixteen, copy_off));
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(smem + umad(lo & kAnsMask, k.entry, copy_off));
         const uint32_t shifted = __funnelshift_r(lo, hi, kAnsBits);      // state >> 8, fits 32 bits
         const uint64_t next = static_cast<uint64_t>((e >> 12) & 0xFFFu) * shifted + (e & 0xFFFu);
         lo = static_cast<uint32_t>(next);
@@ -662,7 +662,7 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
-    const Consts k{1u, 8u, 16u, 65536u};
+    const Consts k{1u, 8u, 4u * kCopies, 65536u};
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes, k);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
 }

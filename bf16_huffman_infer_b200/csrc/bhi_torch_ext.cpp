@@ -193,6 +193,52 @@ void boxed_gemv_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
                             static_cast<int>(B), stream_of(rem)));
 }
 
+// linear_bf16_huffman_prepared(A_rem, A_exp, X, Y(a!), offsets, prepared) -> ()   (up to 128 rows of X)
+void boxed_linear_bf16_huffman_prepared(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
+           blob = arg(stack, 5);
+    LayerView v = layer_of(rem, exp, off);
+    want(X, ScalarType::BFloat16, "X");
+    want(Y, ScalarType::BFloat16, "Y", 2);
+    want(blob, ScalarType::Byte, "prepared");
+    same_device(rem, X, "X");
+    same_device(rem, Y, "Y");
+    same_device(rem, blob, "prepared");
+    STD_TORCH_CHECK(blob.numel() == bhi_huffman_prepared_bytes(), "prepared has the wrong size");
+    const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
+    STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
+    const int64_t B = X.numel() / K;
+    STD_TORCH_CHECK(B <= BHI_MAX_LINEAR_BATCH, "batch_size <= 128");
+    STD_TORCH_CHECK(Y.numel() == B * v.M, "Y must be [batch, M]");
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_linear_bf16_huffman_prepared(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words,
+                                           ptr<const uint16_t>(X), ptr<uint16_t>(Y), ptr<const int32_t>(off),
+                                           ptr<const uint8_t>(blob), v.S, v.M, v.Nc, static_cast<int>(B), stream_of(rem)));
+}
+
+// linear_bf16_ans(A_rem, A_exp, X, Y(a!), offsets, LUT) -> ()   (up to 128 rows of X)
+void boxed_linear_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
+           lut = arg(stack, 5);
+    LayerView v = layer_of(rem, exp, off);
+    want(X, ScalarType::BFloat16, "X");
+    want(Y, ScalarType::BFloat16, "Y", 2);
+    want(lut, ScalarType::Int, "LUT");
+    same_device(rem, X, "X");
+    same_device(rem, Y, "Y");
+    same_device(rem, lut, "LUT");
+    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
+    STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
+    const int64_t B = X.numel() / K;
+    STD_TORCH_CHECK(B <= BHI_MAX_LINEAR_BATCH, "batch_size <= 128");
+    STD_TORCH_CHECK(Y.numel() == B * v.M, "Y must be [batch, M]");
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_linear_bf16_ans(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
+                              ptr<uint16_t>(Y), ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc,
+                              static_cast<int>(B), stream_of(rem)));
+}
+
 // ans_decode(A_rem, A_exp, Y(a!), offsets, LUT) -> ()
 void boxed_ans_decode(StableIValue *stack, uint64_t, uint64_t) {
     Tensor rem = arg(stack, 0), exp = arg(stack, 1), Y = arg(stack, 2), off = arg(stack, 3), lut = arg(stack, 4);
@@ -352,6 +398,8 @@ STABLE_TORCH_LIBRARY(BHI_TORCH_NAMESPACE, m) {
     m.def("huffman_prepare(Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths, Tensor(a!) prepared) -> ()");
     m.def("gemv_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("huffman_decode_prepared(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
+    m.def("linear_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
+    m.def("linear_bf16_ans(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()");
     m.def("set_launch_overlap(int on) -> int");
     // whole-layer encoder
     m.def("huffman_size_pass(Tensor W, int split_k, Tensor code_lengths, Tensor(a!) words_per_row) -> ()");
@@ -374,6 +422,8 @@ STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CUDA, m) {
     m.impl("huffman_prepare", &boxed_huffman_prepare);
     m.impl("gemv_bf16_huffman_prepared", &boxed_gemv_bf16_huffman_prepared);
     m.impl("huffman_decode_prepared", &boxed_huffman_decode_prepared);
+    m.impl("linear_bf16_huffman_prepared", &boxed_linear_bf16_huffman_prepared);
+    m.impl("linear_bf16_ans", &boxed_linear_bf16_ans);
     m.impl("huffman_size_pass", &boxed_huffman_size_pass);
     m.impl("huffman_emit_pass", &boxed_huffman_emit_pass);
     m.impl("ans_size_pass", &boxed_ans_size_pass);

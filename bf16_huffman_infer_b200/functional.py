@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
 
+import os
+
 import torch
 import torch.nn.functional as F
 from torch import Tensor, nn
@@ -28,7 +30,11 @@ from .utils import get_block_size_n, split_bf16
 OP_PER_LANE = 1
 ANS_PRECISION = 8
 SLAB_ROWS = 4096          # rows encoded per slab; 64 padding words follow every slab
-FUSED_MAX_ROWS = 8        # activations with more rows take the decode + GEMM branch
+FUSED_MAX_ROWS = 8        # up to here: fused decode + GEMV; beyond: decode, then a library GEMM (as the reference)
+# Rows up to which the fused decode + tensor-core product (mm_huffman_prepared / mm_ans, at most 128) is used
+# instead of decode + GEMM.  Off by default: on B200 it is correct but slower than decode + library GEMM
+# (its tensor-core instructions are issued for 32 weight rows at a time).  BHI_TENSOR_ROWS=128 turns it on.
+TENSOR_MAX_ROWS = int(os.environ.get("BHI_TENSOR_ROWS", "0"))
 
 __all__ = [
     "linear_huffman",
@@ -133,6 +139,37 @@ def mv_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, LUT: Tensor
     assert A_rem.device == A_exp.device == X.device
     Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
     ops.gemv_bf16_ans(A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(), LUT.contiguous())
+    return Y
+
+
+def mm_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, prepared: Tensor) -> Tensor:
+    """``X @ W.T`` for at most 128 rows of ``X`` from the Huffman-coded ``W``: rows of ``W`` are decoded
+    into shared memory and multiplied there on the tensor cores.  Stands in for the reference's
+    ``huffman_decode`` + ``F.linear`` pair (``functional.py:405-407``) in that range."""
+    if A_rem.dim() == 2:
+        A_rem = A_rem[None, :, :]
+    split_k, M, N = A_rem.shape
+    X = X.view(-1, split_k, N)
+    assert N % 128 == 0
+    assert X.dtype == torch.bfloat16
+    assert A_rem.device == A_exp.device == X.device and A_rem.device.type == "cuda"
+    Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
+    ops.linear_bf16_huffman_prepared(A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(), prepared)
+    return Y
+
+
+def mm_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, LUT: Tensor) -> Tensor:
+    """Same for the rANS-coded ``W`` (stands in for ``ans_decode`` + ``F.linear``, reference
+    ``functional.py:476-478``)."""
+    if A_rem.dim() == 2:
+        A_rem = A_rem[None, :, :]
+    split_k, M, N = A_rem.shape
+    X = X.view(-1, split_k, N)
+    assert N % 128 == 0
+    assert X.dtype == torch.bfloat16
+    assert A_rem.device == A_exp.device == X.device and A_rem.device.type == "cuda"
+    Y = torch.empty((X.size(0), M), dtype=torch.bfloat16, device=A_rem.device)
+    ops.linear_bf16_ans(A_rem.contiguous(), A_exp.contiguous(), X.contiguous(), Y, offsets.contiguous(), LUT.contiguous())
     return Y
 
 
@@ -367,12 +404,12 @@ class CompressedLinear(nn.Module):
         return F.linear(input, self.weight, self.bias)
 
 
-def _linear_compressed(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor], fused) -> Tensor:
+def _linear_compressed(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor], fused, tensor) -> Tensor:
     assert input.dim() >= 2, input
     shape = input.shape
     input = input.flatten(0, -2)
-    if input.size(0) <= FUSED_MAX_ROWS:
-        output = fused(input)
+    if input.size(0) <= max(FUSED_MAX_ROWS, min(TENSOR_MAX_ROWS, 128)):
+        output = fused(input) if input.size(0) <= FUSED_MAX_ROWS else tensor(input)
         if bias is not None:
             output += bias[None, :]
     else:
@@ -381,16 +418,20 @@ def _linear_compressed(input: Tensor, weight: HuffmanWeight, bias: Optional[Tens
 
 
 def linear_huffman(input: Tensor, weight: HuffmanWeight, bias: Optional[Tensor] = None) -> Tensor:
-    """``F.linear`` on a Huffman-coded weight: fused decode+GEMV up to 8 rows, decode then GEMM
-    beyond (reference ``functional.py:390-411``)."""
-    return _linear_compressed(input, weight, bias, lambda x: mv_huffman_prepared(
-        weight.rem, weight.exp, x, weight.offsets, weight.prepared()))
+    """``F.linear`` on a Huffman-coded weight: fused decode+GEMV up to 8 rows, decode then GEMM beyond
+    (reference ``functional.py:390-411``); optionally the fused tensor-core product up to ``TENSOR_MAX_ROWS``."""
+    return _linear_compressed(
+        input, weight, bias,
+        lambda x: mv_huffman_prepared(weight.rem, weight.exp, x, weight.offsets, weight.prepared()),
+        lambda x: mm_huffman_prepared(weight.rem, weight.exp, x, weight.offsets, weight.prepared()))
 
 
 def linear_ans(input: Tensor, weight: ANSWeight, bias: Optional[Tensor] = None) -> Tensor:
     """Same for an rANS-coded weight (reference ``functional.py:447-466``)."""
-    return _linear_compressed(input, weight, bias, lambda x: mv_ans(
-        weight.rem, weight.exp, x, weight.offsets, weight.LUT))
+    return _linear_compressed(
+        input, weight, bias,
+        lambda x: mv_ans(weight.rem, weight.exp, x, weight.offsets, weight.LUT),
+        lambda x: mm_ans(weight.rem, weight.exp, x, weight.offsets, weight.LUT))
 
 
 def _buffers_size(w: nn.Module) -> int:

@@ -74,6 +74,16 @@ def gemv_bf16_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tenso
     _ops.gemv_bf16_huffman_prepared.default(A_rem, A_exp, X, Y, offsets, prepared)
 
 
+def linear_bf16_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
+    """Fused decode + tensor-core product for up to 128 rows of ``X`` (no reference counterpart)."""
+    _ops.linear_bf16_huffman_prepared.default(A_rem, A_exp, X, Y, offsets, prepared)
+
+
+def linear_bf16_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tensor, offsets: Tensor, LUT: Tensor) -> None:
+    """Fused decode + tensor-core product for up to 128 rows of ``X`` (no reference counterpart)."""
+    _ops.linear_bf16_ans.default(A_rem, A_exp, X, Y, offsets, LUT)
+
+
 def huffman_decode_prepared(A_rem: Tensor, A_exp: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
     _ops.huffman_decode_prepared.default(A_rem, A_exp, Y, offsets, prepared)
 

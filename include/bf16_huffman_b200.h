@@ -32,7 +32,8 @@ extern "C" {
 #define BHI_ERR_CUDA 2     /* a CUDA runtime call failed (message holds cudaGetErrorString) */
 #define BHI_ERR_LIMIT 3    /* a size beyond a documented fixed limit */
 
-#define BHI_MAX_BATCH 8
+#define BHI_MAX_BATCH 8            /* rows of X the fused GEMV accepts */
+#define BHI_MAX_LINEAR_BATCH 128   /* rows of X the fused tensor-core product accepts */
 #define BHI_ANS_PRECISION 8
 
 /* Message describing the last error returned on this thread ("" if none). */
@@ -105,6 +106,26 @@ int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_w
 int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
                    uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
                    int split_k, int M, int Nc, void *stream);
+
+/* ---- fused decode + tensor-core product for up to 128 rows of X -----------------------------
+ * Y[b, m] = sum_c X[b, c] * W[m, c] for 1 <= batch <= BHI_MAX_LINEAR_BATCH (meant for 9..128; the
+ * GEMV entry points are faster up to 8).  The reference has no operator for this range: it decodes
+ * the weight to a dense scratch with huffman_decode / ans_decode and calls a library GEMM
+ * (bf16_huffman_infer/functional.py:398-407, 469-478).  These entry points replace that pair of
+ * calls: a set of weight rows is decoded into shared memory and multiplied there by tcgen05.mma
+ * with the accumulator in tensor memory, so the dense weight never reaches HBM.  Accumulation is
+ * FP32 over the whole row, one rounding to BF16 at the end.  X must be 16-byte aligned. */
+int bhi_linear_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                            const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                            const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
+                            const uint8_t *LUT4, const uint8_t *code_lengths,
+                            int split_k, int M, int Nc, int batch, void *stream);
+int bhi_linear_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                     const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                     const uint8_t *prepared, int split_k, int M, int Nc, int batch, void *stream);
+int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                        int split_k, int M, int Nc, int batch, void *stream);
 
 /* Per-stream Huffman code emission as ASCII '0'/'1' characters.
  *   data u8 [streams, n]; LUT u8 [256, 32] code strings (root first, NUL padded);

@@ -128,6 +128,25 @@ class Abi:
         self.check(rc)
         return y
 
+    def linear(self, algo, w, x, prepared=False):
+        """Fused decode + tensor-core product: x bf16 [B <= 128, K] -> bf16 [B, M]."""
+        S, M, Nc = w["rem"].shape
+        B = x.shape[0]
+        y = torch.empty(B, M, dtype=torch.bfloat16, device=x.device)
+        p = self.p
+        if algo == "huffman" and prepared:
+            rc = self.lib.bhi_linear_bf16_huffman_prepared(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
+                                                           p(w["offsets"]), p(self.prepare(w)), S, M, Nc, B, self.stream())
+        elif algo == "huffman":
+            rc = self.lib.bhi_linear_bf16_huffman(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
+                                                  p(w["offsets"]), p(w["LUT1"]), p(w["LUT2"]), p(w["LUT3"]), p(w["LUT4"]),
+                                                  p(w["code_lengths"]), S, M, Nc, B, self.stream())
+        else:
+            rc = self.lib.bhi_linear_bf16_ans(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
+                                              p(w["offsets"]), p(w["LUT"]), S, M, Nc, B, self.stream())
+        self.check(rc)
+        return y
+
     def decode(self, algo, w, prepared=False):
         S, M, Nc = w["rem"].shape
         y = torch.empty(M, S * Nc, dtype=torch.bfloat16, device=w["rem"].device)

@@ -1,5 +1,5 @@
 """The Python surface on a GPU: weight containers, the F.linear hook, both branches (<= 8 rows fused,
-> 8 rows decode + GEMM), bias, model surgery, and the per-stream encode operators."""
+> 8 rows decode + GEMM) and the optional tensor-core branch, bias, model surgery, and the per-stream encode operators."""
 import os
 import sys
 
@@ -53,7 +53,7 @@ def test_linear_hook_both_branches_and_bias(algo):
     lin = CompressedLinear(cw, nn.Parameter(bias.clone())).to(DEV)
     plain = CompressedLinear(cw, None).to(DEV)
     assert (lin.out_features, lin.in_features) == (M, K)
-    for shape in [(1, K), (8, K), (2, 3, K), (9, K), (4, 8, K)]:
+    for shape in [(1, K), (8, K), (2, 3, K), (9, K), (4, 8, K), (128, K), (5, 26, K)]:
         rows = int(np.prod(shape[:-1]))
         x = make_input(rows, K, 3).view(shape)
         with torch.no_grad():
@@ -68,6 +68,29 @@ def test_linear_hook_both_branches_and_bias(algo):
         else:
             # decode + GEMM branch: bias inside the GEMM epilogue, one rounding
             assert rel_err(y.float().cpu().view(-1, M).numpy(), (ref0 + bias.double()).numpy()) <= TOL
+
+
+@pytest.mark.parametrize("algo", ["huffman", "ans"])
+def test_optional_tensor_core_branch(algo, monkeypatch):
+    """With TENSOR_MAX_ROWS raised, 9..128 rows go through the fused tensor-core product."""
+    import bf16_huffman_infer_b200.functional as fn
+    M, K = 256, 1024
+    W = make_weight(M, K, 7)
+    bias = make_weight(1, M, 8)[0]
+    cls = fn.HuffmanWeight if algo == "huffman" else fn.ANSWeight
+    lin = fn.CompressedLinear(cls.compress(W), nn.Parameter(bias.clone())).to(DEV)
+    calls = []
+    for name in ("mm_huffman_prepared", "mm_ans"):
+        real = getattr(fn, name)
+        monkeypatch.setattr(fn, name, lambda *a, _real=real, **k: (calls.append(1), _real(*a, **k))[1])
+    monkeypatch.setattr(fn, "TENSOR_MAX_ROWS", 128)
+    for rows in (9, 64, 128, 130):
+        x = make_input(rows, K, rows)
+        with torch.no_grad():
+            y = lin(x.to(DEV))
+        ref = x.double() @ W.double().T + bias.double()
+        assert rel_err(y.float().cpu().numpy(), ref.numpy()) <= 2 * TOL          # bias added after a first BF16 rounding
+    assert len(calls) == 3                                                        # 130 rows: decode + GEMM
 
 
 def test_per_stream_operators_match_oracle():
