@@ -68,9 +68,12 @@ def fuse_shapes(shapes):
 def layer_shapes(name):
     if name.endswith("+fused"):
         return fuse_shapes(layer_shapes(name[:-6]))
-    if name.startswith("layer:"):                      # a single matrix, e.g. layer:4096x4096 (for profiler captures)
+    if name.startswith("layer:"):                      # a single matrix, e.g. layer:4096x4096
         m, k = (int(v) for v in name[6:].split("x"))
         return [("layers.0.single", m, k)]
+    if name.startswith("stack:"):                      # N distinct matrices of one shape, e.g. stack:8x12288x4096:
+        n, m, k = (int(v) for v in name[6:].split("x"))  # small, yet larger than L2 (for profiler captures)
+        return [(f"layers.{i}.single", m, k) for i in range(n)]
     L, h, inter, qh, kvh, hd, vocab = WORKLOADS[name]
     per_layer = [("q_proj", qh * hd, h), ("k_proj", kvh * hd, h), ("v_proj", kvh * hd, h), ("o_proj", h, qh * hd),
                  ("gate_proj", inter, h), ("up_proj", inter, h), ("down_proj", h, inter)]
@@ -129,7 +132,7 @@ class ClockSampler:
 
 
 # ---- the CPU arm (oracle): bounded sample of the workload ------------------------------------------------
-def cpu_arm(workload, algo, batch, budget_s=12.0):
+def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference"):
     """Times the CPU restatement of the fused path on the first matrices of the stack, in model order,
     until about `budget_s` seconds of CPU work have been measured, and scales to a whole step by
     weight count."""
@@ -142,7 +145,7 @@ def cpu_arm(workload, algo, batch, budget_s=12.0):
         hist = oracle.histogram(bits)
         if a == "huffman":
             enc = LUTHuffmanEncoder()
-            enc.build_lut(hist)
+            enc.build_lut(hist, method=tables)
             return {"LUT1": enc.LUT1, "LUT2": enc.LUT2, "LUT3": enc.LUT3, "LUT4": enc.LUT4,
                     "code_lengths": enc.code_lengths, "code_values": enc.code_values}
         enc = RANSEncoder([int(v) for v in hist], precision=8)
@@ -236,8 +239,10 @@ def run_step(mods, meta, xs, batch):
 
 def ours(args, rank, world, dev):
     import torch.distributed as dist
+    from bf16_huffman_infer_b200 import set_huffman_tables
 
     t_setup = time.time()
+    set_huffman_tables(args.tables)
     mods, meta = build_stack(args.workload, args.algo, rank, world, dev)
     hidden = meta[0]["K"]
     B = args.batch
@@ -308,8 +313,9 @@ def ours(args, rank, world, dev):
         "data": "synthetic", "impl": "ours",
         "config": {
             "workload": f"{args.workload}-shape linear stack ({len(mods)} matrices, {sum(m['M'] * m['K'] for m in meta) / 1e9:.2f}G weights), "
-                        f"batch {B}, algo {args.algo}, rows sharded over {world} GPU(s)",
-            "batch": B, "algo": args.algo, "l2": "inputs larger than L2 (the step streams every compressed weight once)",
+                        f"batch {B}, algo {args.algo}"
+                        + (f" ({args.tables} table builder)" if args.algo != "ans" else "") + f", rows sharded over {world} GPU(s)",
+            "batch": B, "algo": args.algo, "tables": args.tables, "l2": "inputs larger than L2 (the step streams every compressed weight once)",
             "compressed_bytes_per_rank": int(sum(m["bytes"] for m in meta)),
             "ratio": sum(m["bytes"] for m in meta) / (2.0 * sum(m["local_rows"] * m["K"] for m in meta)),
             "setup_s": round(setup_s, 1),
@@ -378,11 +384,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-8b+fused",
                     help="one of %s, optionally with +fused (q/k/v and gate/up stacked into one launch each), "
-                         "or layer:MxK for a single matrix" % sorted(WORKLOADS))
+                         "or layer:MxK for a single matrix, or stack:NxMxK for N distinct matrices of one shape" % sorted(WORKLOADS))
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
+    ap.add_argument("--tables", default="escape", choices=["escape", "reference"],
+                    help="Huffman table builder: 'escape' (this library's, near-entropy on every histogram) or "
+                         "'reference' (the reference's own code, bit-identical compressed bytes); both fill the "
+                         "reference's table format")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-reference-tables", action="store_true",
+                    help="skip the second run with the reference's table builder")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -423,11 +435,24 @@ def main():
     line, mods, meta, xs = ours(args, rank, world, dev)
     del mods, xs
     torch.cuda.empty_cache()
+    if world == 1 and args.tables == "escape" and args.algo != "ans" and not args.no_reference_tables:
+        # the same stack encoded with the reference's own table builder, timed the same way
+        free, total = torch.cuda.mem_get_info(dev)
+        if line["config"]["compressed_bytes_per_rank"] * 1.3 < free:
+            alt = argparse.Namespace(**{**vars(args), "tables": "reference"})
+            other, m2, _, x2 = ours(alt, rank, world, dev)
+            del m2, x2
+            torch.cuda.empty_cache()
+            line["reference_tables"] = {"value": other["value"], "unit": "tokens/s", "ms_per_step": other["ms_per_step"],
+                                        "ratio": other["config"]["ratio"], "roofline_frac": other["roofline"]["frac"],
+                                        "e2e": other["e2e"]["value"]}
+        else:
+            line["reference_tables"] = {"unavailable": "not enough free device memory for a second stack"}
     if rank == 0:
         if world == 1 and not args.no_dense:
             line["dense_bf16_torch"] = dense_arm(args, dev)
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch)
+            line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch, tables=args.tables)
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

@@ -35,6 +35,18 @@ FUSED_MAX_ROWS = 8        # up to here: fused decode + GEMV; beyond: decode, the
 # instead of decode + GEMM.  Off by default: on B200 it is correct but slower than decode + library GEMM
 # (its tensor-core instructions are issued for 32 weight rows at a time).  BHI_TENSOR_ROWS=128 turns it on.
 TENSOR_MAX_ROWS = int(os.environ.get("BHI_TENSOR_ROWS", "0"))
+# Which prefix code HuffmanWeight.compress builds: "reference" reproduces the reference's tables (and so its
+# compressed bytes) exactly; "escape" uses the escape-byte builder of huffman.py (same table format, readable
+# by any decoder of the format, near-entropy on every histogram).  See set_huffman_tables().
+HUFFMAN_TABLES = os.environ.get("BHI_HUFFMAN_TABLES", "reference")
+
+
+def set_huffman_tables(method: str) -> str:
+    """Choose the table builder used by later ``HuffmanWeight.compress`` calls; returns the previous choice."""
+    global HUFFMAN_TABLES
+    assert method in ("reference", "escape"), method
+    previous, HUFFMAN_TABLES = HUFFMAN_TABLES, method
+    return previous
 
 __all__ = [
     "linear_huffman",
@@ -46,6 +58,7 @@ __all__ = [
     "convert_all_linear",
     "convert",
     "fuse_sibling_linears",
+    "set_huffman_tables",
 ]
 
 # projections that read the same input inside one block of the usual decoder architectures
@@ -237,7 +250,7 @@ class HuffmanWeight(nn.Module):
     def get_codec(cls, a: Tensor) -> LUTHuffmanEncoder:
         """Code tables from the exponent histogram of ``a`` (reference ``functional.py:110-117``)."""
         codec = LUTHuffmanEncoder()
-        codec.build_lut(_exp_histogram(a.to(_work_device(a))))
+        codec.build_lut(_exp_histogram(a.to(_work_device(a))), method=HUFFMAN_TABLES)
         return codec
 
     @classmethod
@@ -574,13 +587,19 @@ def fuse_sibling_linears(model: nn.Module, groups=SIBLING_GROUPS, algo: str = "h
 
 
 def convert_all_linear(model: nn.Module, min_out_features: int = 4096, progress: bool = True,
-                       algo: str = "huffman", fuse_siblings: bool = False) -> None:
+                       algo: str = "huffman", fuse_siblings: bool = False, huffman_tables: Optional[str] = None) -> None:
     """Replace, in place, every ``nn.Linear`` with at least ``min_out_features`` outputs
-    (reference ``functional.py:378-387``).  ``fuse_siblings=True`` (not in the reference) first stacks
-    q/k/v and gate/up projections into single compressed weights, see :class:`FusedCompressedLinear`."""
-    if fuse_siblings:
-        fuse_sibling_linears(model, algo=algo, progress=progress)
-    targets = [name for name, mod in model.named_modules()
-               if isinstance(mod, nn.Linear) and mod.out_features >= min_out_features]
-    for name in tqdm(targets, disable=not progress):
-        model.set_submodule(name, convert(model.get_submodule(name), name, algo=algo))
+    (reference ``functional.py:378-387``).  Not in the reference: ``fuse_siblings=True`` first stacks
+    q/k/v and gate/up projections into single compressed weights (:class:`FusedCompressedLinear`);
+    ``huffman_tables`` picks the table builder for this call (:func:`set_huffman_tables`)."""
+    previous = set_huffman_tables(huffman_tables) if huffman_tables is not None else None
+    try:
+        if fuse_siblings:
+            fuse_sibling_linears(model, algo=algo, progress=progress)
+        targets = [name for name, mod in model.named_modules()
+                   if isinstance(mod, nn.Linear) and mod.out_features >= min_out_features]
+        for name in tqdm(targets, disable=not progress):
+            model.set_submodule(name, convert(model.get_submodule(name), name, algo=algo))
+    finally:
+        if previous is not None:
+            set_huffman_tables(previous)

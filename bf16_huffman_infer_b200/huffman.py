@@ -154,6 +154,87 @@ def _repair_collisions(freqs: Dict[int, float], max_bits: int) -> Dict[int, floa
     raise AssertionError("table-collision repair did not converge")
 
 
+# ---- escape-byte builder: an alternative code for the same tables ---------------------------------
+# The byte-decomposed tables need every code longer than 8 bits to be recognisable from its SECOND byte
+# alone, whatever its first byte was.  The reference reaches that by perturbing frequencies until the
+# plain Huffman code happens to satisfy it, which for some histograms lengthens the frequent codes a
+# lot.  This builder satisfies the constraint by construction instead: frequent symbols get a
+# length-limited (<= 8 bits) optimal code together with ONE escape leaf, padded to exactly 8 bits; all
+# the other symbols hang below that escape byte with a second length-limited (<= 8 bits) optimal code,
+# so they are told apart by the second byte and no code exceeds 16 bits.  The split point is chosen by
+# exhaustive search for the smallest total cost.  The tables it yields have the reference's layout
+# and semantics (any decoder of the format reads them); only the code itself differs from the one the
+# reference's builder would pick, so the compressed bytes differ too.
+
+def _limited_lengths(weights: Sequence[float], limit: int) -> List[int]:
+    """Optimal code lengths with no length above ``limit`` (package-merge); weights need not be sorted."""
+    n = len(weights)
+    if n == 0:
+        return []
+    if n == 1:
+        return [1]
+    assert n <= (1 << limit), "too many symbols for the length limit"
+    order = sorted(range(n), key=lambda i: (weights[i], i))
+    leaves = [(weights[i], (i,)) for i in order]
+    level = list(leaves)
+    for _ in range(limit - 1):
+        packages = [(level[j][0] + level[j + 1][0], level[j][1] + level[j + 1][1]) for j in range(0, len(level) - 1, 2)]
+        level = sorted(leaves + packages, key=lambda t: t[0])      # stable: leaves before packages of equal weight
+    lengths = [0] * n
+    for _, members in level[: 2 * n - 2]:
+        for i in members:
+            lengths[i] += 1
+    return lengths
+
+
+def _canonical_paths(lengths: Dict[int, int]) -> Dict[int, str]:
+    """Root-first path strings of a canonical prefix code: shorter codes first, then ascending key."""
+    paths: Dict[int, str] = {}
+    code = 0
+    prev = 0
+    for key in sorted(lengths, key=lambda k: (lengths[k], k)):
+        n = lengths[key]
+        code <<= n - prev
+        paths[key] = format(code, "b").zfill(n)
+        code += 1
+        prev = n
+    return paths
+
+
+def escape_byte_code(freqs: Dict[int, float]) -> Dict[int, Tuple[int, int]]:
+    """``{symbol: (length, value)}`` (first path bit in bit 0) of the escape-byte code for ``freqs``."""
+    syms = sorted(freqs, key=lambda s: (-freqs[s], s))
+    n = len(syms)
+    if n == 0:
+        return {}
+    ESC = -1
+    best = None
+    for top in range(max(1, n - 255), n + 1):
+        rest = n - top
+        if rest == 1 or top + (1 if rest else 0) > 256:
+            continue                                       # a lone escaped symbol is just a 256th leaf: covered by top + 1
+        upper = syms[:top] + ([ESC] if rest else [])
+        w_upper = [freqs[s] for s in syms[:top]] + ([sum(freqs[s] for s in syms[top:])] if rest else [])
+        l_upper = _limited_lengths(w_upper, 8)
+        l_lower = _limited_lengths([freqs[s] for s in syms[top:]], 8)
+        cost = sum(w * l for w, l in zip(w_upper[:top], l_upper[:top])) + sum(freqs[s] * (8 + l) for s, l in zip(syms[top:], l_lower))
+        if best is None or cost < best[0]:
+            best = (cost, top, dict(zip(upper, l_upper)), dict(zip(syms[top:], l_lower)))
+    _, top, l_upper, l_lower = best
+    # canonical order puts the escape leaf last among the leaves of its length (ESC sorts as the largest key below)
+    upper_paths = _canonical_paths({(256 if k == ESC else k): v for k, v in l_upper.items()})
+    codes: Dict[int, Tuple[int, int]] = {}
+    for k, path in upper_paths.items():
+        if k != 256:
+            codes[k] = (len(path), int(path[::-1], 2))
+    if l_lower:
+        esc = upper_paths[256].ljust(8, "0")                # pad the escape to a whole byte
+        for k, path in _canonical_paths(l_lower).items():
+            full = esc + path
+            codes[k] = (len(full), int(full[::-1], 2))
+    return codes
+
+
 class LUTHuffmanEncoder:
     """Drop-in for the reference class of the same name (``huffman.py:23-397``).
 
@@ -174,10 +255,17 @@ class LUTHuffmanEncoder:
         self.code_values = np.zeros(256, dtype=np.uint32)
 
     # -- table construction -------------------------------------------------------------
-    def build_lut(self, frequencies: Union[np.ndarray, Sequence[int], "torch.Tensor"]) -> None:
+    def build_lut(self, frequencies: Union[np.ndarray, Sequence[int], "torch.Tensor"], method: str = "reference") -> None:
+        """``method='reference'`` reproduces the reference's code exactly; ``'escape'`` builds the
+        escape-byte code (same table format, shorter frequent codes when the reference's repair loop
+        would have distorted them; no counterpart in the reference)."""
         if torch is not None and torch.is_tensor(frequencies):
             frequencies = frequencies.cpu().numpy()
         freqs = {i: float(frequencies[i]) for i in range(256) if frequencies[i] > 0}
+        if method == "escape":
+            self._install(escape_byte_code(freqs))
+            return
+        assert method == "reference", method
         final = _repair_collisions(freqs, self.max_code_length)
         self._install(_huffman_paths(final))
 

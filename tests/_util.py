@@ -28,10 +28,10 @@ def bits_of(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy().view(np.uint16)
 
 
-def huffman_tables(hist):
+def huffman_tables(hist, method="reference"):
     from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
     enc = LUTHuffmanEncoder()
-    enc.build_lut(np.asarray(hist))
+    enc.build_lut(np.asarray(hist), method=method)
     return {"LUT1": enc.LUT1, "LUT2": enc.LUT2, "LUT3": enc.LUT3, "LUT4": enc.LUT4,
             "code_lengths": enc.code_lengths, "code_values": enc.code_values}, enc
 
@@ -43,8 +43,8 @@ def ans_tables(hist):
     return {"freq": np.array(enc.freq, np.uint32), "cum": np.array(enc.cum, np.uint32), "LUT": lut.view(np.int32)}, enc
 
 
-def tables_for(algo, hist):
-    return huffman_tables(hist)[0] if algo == "huffman" else ans_tables(hist)[0]
+def tables_for(algo, hist, method="reference"):
+    return huffman_tables(hist, method)[0] if algo == "huffman" else ans_tables(hist)[0]
 
 
 def load_json(name):

@@ -105,6 +105,35 @@ def test_pathological_tables_long_codes(abi):
             abi.set_path(prev)
 
 
+@pytest.mark.parametrize("M,K,S,seed", [(384, 1024, 2, 4), (512, 4096, 1, 0), (128, 12288, 3, 0)])
+def test_escape_byte_tables_on_every_path(abi, M, K, S, seed):
+    """Tables from the alternative (escape-byte) builder: device encoder bytes equal the oracle's, all
+    decode paths are bit-exact, GEMV and the tensor-core product stay within tolerance."""
+    W = make_weight(M, K, seed)
+    Wb = bits_of(W)
+    tabs = tables_for("huffman", oracle.histogram(Wb), method="escape")
+    rem, exp, offsets, L = oracle.compress(Wb, "huffman", tabs, split_k=S)
+    g_rem, g_exp, g_off, g_rows = abi.encode("huffman", W.to(DEV), S, tabs)
+    assert (g_rows.cpu().numpy() == L).all() and (g_off.cpu().numpy() == offsets).all()
+    assert (g_rem.cpu().numpy() == rem).all() and (g_exp.cpu().numpy() == exp).all()
+    w = to_device(dict(rem=rem, exp=exp, offsets=offsets, **{k: tabs[k] for k in ("LUT1", "LUT2", "LUT3", "LUT4", "code_lengths")}), DEV)
+    X = make_input(8, K, seed)
+    ref = oracle.matvec(Wb, bits_of(X))
+    for path in (0, 1):
+        prev = abi.set_path(path)
+        try:
+            assert (bits_of(abi.decode("huffman", w).cpu()) == Wb).all()
+            assert (bits_of(abi.decode("huffman", w, prepared=True).cpu()) == Wb).all()
+            for B in (1, 8):
+                y = abi.gemv("huffman", w, X[:B].to(DEV), prepared=True).float().cpu().numpy()
+                assert rel_err(y, ref[:B]) <= TOL
+        finally:
+            abi.set_path(prev)
+    X = make_input(24, K, seed + 1)
+    y = abi.linear("huffman", w, X.to(DEV), prepared=True).float().cpu().numpy()
+    assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL
+
+
 def test_argument_errors_are_reported(abi):
     import ctypes as C
     z = torch.zeros(64, dtype=torch.int32, device=DEV)

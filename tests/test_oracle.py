@@ -83,6 +83,19 @@ def test_oracle_roundtrip_bit_exact(algo, M, K, S, seed):
     assert (back == W).all()
 
 
+@pytest.mark.parametrize("M,K,S,seed", [(128, 512, 1, 0), (128, 384, 3, 3), (4100, 128, 1, 4)])
+def test_oracle_roundtrip_with_escape_byte_tables(M, K, S, seed):
+    """The format does not care which prefix code fills the tables: the alternative builder's code
+    round-trips through the same encoder and decoder, and is never larger."""
+    W = bits_of(make_weight(M, K, seed))
+    hist = oracle.histogram(W)
+    tabs = tables_for("huffman", hist, method="escape")
+    rem, exp, offsets, _ = oracle.compress(W, "huffman", tabs, split_k=S)
+    assert (oracle.decode("huffman", rem, exp, offsets, tabs) == W).all()
+    _, exp_ref, _, _ = oracle.compress(W, "huffman", tables_for("huffman", hist), split_k=S)
+    assert exp.size <= exp_ref.size
+
+
 def test_oracle_rem_permutation_and_split():
     W = bits_of(make_weight(128, 256, 7))
     rem, exp = oracle.split(W)

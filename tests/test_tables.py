@@ -58,6 +58,66 @@ def test_prefix_free_and_table_consistent():
                 assert got == sym, (rec["name"], sym, code)
 
 
+def _escape_histograms():
+    rng = np.random.default_rng(0)
+    hists = [np.array(rec["hist"], np.int64) for rec in TABLES]
+    one = np.zeros(256, np.int64); one[120] = 77
+    two = np.zeros(256, np.int64); two[[3, 200]] = (5, 900)
+    flat = np.full(256, 10, np.int64)                                     # 256 equally likely symbols
+    geo = (2.0 ** -np.arange(256) * 1e15).astype(np.int64) + 1            # every symbol present, steep tail
+    wide = rng.integers(1, 1000, 256).astype(np.int64)
+    few_common = np.ones(256, np.int64); few_common[100:110] = 10 ** 9
+    return hists + [one, two, flat, geo, wide, few_common]
+
+
+def test_escape_byte_code_is_decodable_and_short():
+    """The alternative builder: prefix-free, at most 16 bits, decodable by the byte cascade, and never
+    longer on average than the reference's code for the same histogram."""
+    from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
+    for hist in _escape_histograms():
+        enc = LUTHuffmanEncoder()
+        enc.build_lut(hist, method="escape")
+        present = [s for s in range(256) if hist[s] > 0]
+        assert sorted(enc.huffman_codes) == present
+        lens = enc.code_lengths.astype(np.int64)
+        assert lens[present].min() >= 1 and lens.max() <= 16
+        assert sum(2.0 ** -int(lens[s]) for s in present) <= 1.0 + 1e-12     # Kraft
+        paths = sorted(code[::-1] for code in enc.huffman_codes.values())     # root-first strings
+        assert all(not b.startswith(a) for a, b in zip(paths, paths[1:])), "not prefix-free"
+        assert (enc.LUT3 == 255).all() and (enc.LUT4 == 255).all()
+        tabs = (enc.LUT1, enc.LUT2, enc.LUT3, enc.LUT4)
+        for sym, code in enc.huffman_codes.items():
+            if sym == 255:
+                continue
+            v, n = int(code, 2), len(code)
+            for fill in (0, 0xFFFFFFFF, 0x5A5A5A5A):
+                window = (v | (fill << n)) & 0xFFFFFFFF
+                got = next((int(t[(window >> (8 * k)) & 0xFF]) for k, t in enumerate(tabs)
+                            if t[(window >> (8 * k)) & 0xFF] != 255), None)
+                assert got == sym, (sym, code)
+        try:
+            ref = LUTHuffmanEncoder()
+            ref.build_lut(hist)
+        except AssertionError:
+            continue                                                          # the reference's repair loop gives up here
+        cost = lambda e: float((hist * e.code_lengths.astype(np.int64)).sum())
+        assert cost(enc) <= cost(ref) * 1.001
+
+
+def test_escape_byte_code_is_near_entropy_on_weight_histograms():
+    from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
+    for rec in TABLES:
+        hist = np.array(rec["hist"], np.float64)
+        if (hist > 0).sum() < 2:
+            continue
+        p = hist[hist > 0] / hist.sum()
+        entropy = float(-(p * np.log2(p)).sum())
+        enc = LUTHuffmanEncoder()
+        enc.build_lut(hist, method="escape")
+        avg = float((hist * enc.code_lengths).sum() / hist.sum())
+        assert avg <= entropy + 1.0, (rec["name"], avg, entropy)             # Huffman bound; the escape costs rare symbols only
+
+
 def test_slow_codecs_roundtrip():
     from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
     from bf16_huffman_infer_b200.ans import RANSEncoder
