@@ -179,12 +179,13 @@ def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference"):
 
 
 # ---- our arm ------------------------------------------------------------------------------------------
-def build_stack(workload, algo, rank, world, dev, verify=True):
+def build_stack(workload, algo, rank, world, dev, verify=True, exchange="peer"):
     """Compress every matrix of the stack on the device; returns modules, shapes and byte counts."""
     from bf16_huffman_infer_b200 import ANSWeight, CompressedLinear, HuffmanWeight
-    from bf16_huffman_infer_b200.tensor_parallel import RowShardedLinear, shard_rows
+    from bf16_huffman_infer_b200.tensor_parallel import PeerArena, PeerRowShardedLinear, RowShardedLinear, shard_rows
 
     mods, meta = [], []
+    arena = PeerArena(dev) if world > 1 and exchange == "peer" else None
     for idx, (name, M, K) in enumerate(layer_shapes(workload)):
         g = torch.Generator(device=dev).manual_seed(idx)
         W = (torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16)
@@ -202,7 +203,12 @@ def build_stack(workload, algo, rank, world, dev, verify=True):
             lo, hi = (M * rank // world, M * (rank + 1) // world)
             assert torch.equal(cw.get_weight().view(torch.int16), W[lo:hi].view(torch.int16)), f"{name}: decode is not bit-exact"
         lin = CompressedLinear(cw, None)
-        mod = RowShardedLinear(lin, M) if world > 1 else lin
+        if world == 1:
+            mod = lin
+        elif arena is not None:
+            mod = PeerRowShardedLinear(lin, M, arena)
+        else:
+            mod = RowShardedLinear(lin, M)
         mods.append(mod)
         info = {"name": name, "M": M, "K": K, "local_rows": cw.shape[0], "bytes": cw.nbytes(), "algo": cw.algo}
         if "+" in name:                                   # stacked siblings: remember where the first one ends
@@ -213,6 +219,8 @@ def build_stack(workload, algo, rank, world, dev, verify=True):
                 info["first_rows"] = inter_
         meta.append(info)
         del W
+    if arena is not None:
+        arena.commit()
     return mods, meta
 
 
@@ -243,7 +251,7 @@ def ours(args, rank, world, dev):
 
     t_setup = time.time()
     set_huffman_tables(args.tables)
-    mods, meta = build_stack(args.workload, args.algo, rank, world, dev)
+    mods, meta = build_stack(args.workload, args.algo, rank, world, dev, exchange=args.exchange)
     hidden = meta[0]["K"]
     B = args.batch
     g = torch.Generator().manual_seed(12345)
@@ -319,6 +327,9 @@ def ours(args, rank, world, dev):
             "compressed_bytes_per_rank": int(sum(m["bytes"] for m in meta)),
             "ratio": sum(m["bytes"] for m in meta) / (2.0 * sum(m["local_rows"] * m["K"] for m in meta)),
             "setup_s": round(setup_s, 1),
+            "exchange": ("none (one GPU)" if world == 1 else
+                         "results stored into every rank's buffer by the kernel's epilogue (peer memory over NVLink)"
+                         if args.exchange == "peer" else "NCCL all-gather after every matrix"),
         },
         "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(x_host.numel() * 2),
                 "d2h_bytes_per_step": int(y_host.numel() * 2)},
@@ -390,6 +401,8 @@ def main():
                     help="Huffman table builder: 'escape' (this library's, near-entropy on every histogram) or "
                          "'reference' (the reference's own code, bit-identical compressed bytes); both fill the "
                          "reference's table format")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="with more than one GPU: how the row slices of every matrix are put together")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

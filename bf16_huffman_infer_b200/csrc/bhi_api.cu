@@ -110,6 +110,33 @@ static int run_linear(const Layer &L, const typename Codec::Args &targs, const u
     return gemm_launch<Codec>(L, targs, prepared, X, Y, B, st);
 }
 
+template <class Codec>
+static int run_exchange(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X, int B,
+                        const bhi_exchange_t *ex, cudaStream_t st) {
+    BHI_REQUIRE(X && ex, "null activation buffer or exchange descriptor");
+    BHI_REQUIRE(B >= 1 && B <= BHI_MAX_BATCH, "batch must be in [1, 8]");
+    BHI_REQUIRE(ex->world >= 1 && ex->world <= BHI_MAX_PEERS && ex->rank >= 0 && ex->rank < ex->world, "bad world / rank");
+    BHI_REQUIRE(ex->row_base >= 0 && ex->M_total >= ex->row_base + L.M, "rows outside the full output");
+    BHI_REQUIRE(ex->launches && aligned(ex->launches, 4), "null or unaligned launch counter");
+    BHI_REQUIRE(aligned(X, 4), "X must be 4-byte aligned");
+    BHI_REQUIRE(aligned(L.rem, 16) && aligned(L.exp, 16) && aligned(prepared, 16), "weight buffers must be 16-byte aligned");
+    PeerSet peers{};
+    for (int r = 0; r < ex->world; r++) {
+        BHI_REQUIRE(ex->y[r] && ex->ready[r] && ex->done[r], "null peer pointer");
+        BHI_REQUIRE(aligned(ex->y[r], 2) && aligned(ex->ready[r], 4) && aligned(ex->done[r], 4), "unaligned peer pointer");
+        peers.y[r] = ex->y[r];
+        peers.ready[r] = ex->ready[r];
+        peers.done[r] = ex->done[r];
+    }
+    peers.launches = ex->launches;
+    peers.world = ex->world;
+    peers.rank = ex->rank;
+    peers.row_base = ex->row_base;
+    peers.m_total = ex->M_total;
+    int rc = staged_exchange<Codec>(L, targs, prepared, X, peers, B, st);
+    return rc == kStagedDeclined ? fail(BHI_ERR_ARG, "shape not supported by the exchange kernel") : rc;
+}
+
 static int check_enc(const void *W, int M, int K, int S) {
     BHI_REQUIRE(W, "null weight");
     BHI_REQUIRE(M >= 1 && K >= 128 && S >= 1 && K % S == 0, "bad shape");
@@ -243,6 +270,27 @@ int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
     AnsArgs t{LUT};
     return run_linear<AnsCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_gemv_bf16_huffman_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                   const uint16_t *X, const int32_t *offsets, const uint8_t *prepared,
+                                   int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    const uint8_t *ex = prepared + kPairEntries * 4;
+    HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
+    return run_exchange<HuffCodec>(L, t, prepared, X, batch, exchange, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT,
+                               int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    AnsArgs t{LUT};
+    return run_exchange<AnsCodec>(L, t, nullptr, X, batch, exchange, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,

@@ -174,6 +174,8 @@ struct GemvSink {
         for (int b = 0; b < B; b++) acc[b] = make_float2(0.f, 0.f);
     }
     __device__ __forceinline__ void begin_record(int) {}
+    __device__ __forceinline__ void after_wait(int) {}        // right after the wait for the previous kernel
+    __device__ __forceinline__ void finish_kernel() {}        // last thing the kernel does
     __device__ __forceinline__ void put(const Consts &k, int gblk, uint32_t w0, uint32_t w1) {
         // low half: w << 16 as a multiply (FMA pipe); high half: one mask
         const float2 f0 = make_float2(__uint_as_float(w0 * k.shift16), bf16hi_to_f32(w0));
@@ -208,11 +210,121 @@ struct DenseSink {
     __device__ __forceinline__ void stage(uint8_t *, int, int) {}
     __device__ __forceinline__ void reset(int lane) { out += lane; }
     __device__ __forceinline__ void begin_record(int m) { row = out + static_cast<int64_t>(m) * row_pairs; }
+    __device__ __forceinline__ void after_wait(int) {}
+    __device__ __forceinline__ void finish_kernel() {}
     __device__ __forceinline__ void put(const Consts &, int gblk, uint32_t w0, uint32_t w1) {
         row[gblk * 64] = w0;
         row[gblk * 64 + 32] = w1;
     }
     __device__ __forceinline__ void finish_row(int, int) {}
+};
+
+// ---- row-sharded GEMV whose epilogue is the all-gather ------------------------------------------------
+// Every rank computes the rows [row_base, row_base + M) of Y [B, M_total] and needs all of it.  Instead
+// of a collective after the kernel, the lanes that hold a finished dot product store it straight into
+// the Y buffer of every rank (plain stores to peer-mapped pointers over NVLink; lane r serves rank r).
+// Three counter words per layer and rank make that safe without any other kernel:
+//   ready  - each rank adds 1 on every peer when its launch may be written to (its earlier consumers of
+//            Y are done: the add comes after the wait for the previous kernel in the stream); a warp
+//            checks its own copy (>= world * launch number) before its first remote store;
+//   done   - each CTA adds 1 on every peer after its stores (release at system scope); the kernel does
+//            not end before the local copy shows world * grid * launch number, so whatever runs next
+//            on the stream sees the whole of Y;
+//   launches (local) - how often this layer has run; written by the one waiting thread at the end.
+// Both waits are bounded; on expiry the status word is set (8 = peers not ready, 9 = peers not done)
+// and the kernel carries on.
+constexpr int kMaxPeers = BHI_MAX_PEERS;
+
+struct PeerSet {
+    uint16_t *y[kMaxPeers];
+    uint32_t *ready[kMaxPeers];
+    uint32_t *done[kMaxPeers];
+    uint32_t *launches;
+    int world, rank, row_base, m_total;
+};
+
+__device__ __forceinline__ void red_release_sys_add(uint32_t *p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// waits until the counter has reached `target` (wrap-safe); false when a second has passed without it
+constexpr uint64_t kPeerWaitNs = 1000ull * 1000ull * 1000ull;
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool counter_wait_bounded(const uint32_t *p, uint32_t target) {
+    if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 0; i < kSpinLimit; i++) {            // the iteration bound is a second line of defence
+        if (static_cast<int32_t>(ld_relaxed_sys(p) - target) >= 0) {
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            return true;
+        }
+        if ((i & 15u) == 15u && global_ns() - t0 > kPeerWaitNs) return false;
+        __nanosleep(40);
+    }
+    return false;
+}
+
+// a[i] without indexing the array by a register (that would move the whole kernel-parameter struct to
+// local memory, accumulators included)
+template <class T>
+__device__ __forceinline__ T pick(T const (&a)[kMaxPeers], int i) {
+    T v = a[0];
+#pragma unroll
+    for (int r = 1; r < kMaxPeers; r++)
+        if (i == r) v = a[r];
+    return v;
+}
+
+template <int B, bool kXS>
+struct ExchangeSink : GemvSink<B, kXS> {
+    using Base = GemvSink<B, kXS>;
+    PeerSet peers;
+    uint16_t *dst;          // this lane's destination rank's Y (lanes >= world: unused)
+    uint32_t launch_no;     // 1-based number of this launch of the layer
+    bool peers_ready;
+
+    __device__ __forceinline__ void after_wait(int lane) {
+        launch_no = *reinterpret_cast<const volatile uint32_t *>(peers.launches) + 1u;   // written by this layer's previous launch
+        peers_ready = false;
+        dst = pick(peers.y, lane < peers.world ? lane : peers.rank);
+        if (blockIdx.x == 0 && threadIdx.x < peers.world) red_release_sys_add(pick(peers.ready, threadIdx.x), 1u);
+    }
+    __device__ __forceinline__ void finish_row(int m, int lane) {
+        if (!peers_ready) {
+            if (!counter_wait_bounded(pick(peers.ready, peers.rank), launch_no * peers.world) && lane == 0) atomicExch(&g_staged_status, 8);
+            peers_ready = true;
+        }
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            const float v = warp_sum(Base::acc[b].x + Base::acc[b].y);          // every lane holds the sum
+            if (lane < peers.world) dst[static_cast<int64_t>(b) * peers.m_total + peers.row_base + m] = f32_to_bf16_rn(v);
+            Base::acc[b] = make_float2(0.f, 0.f);
+        }
+    }
+    __device__ __forceinline__ void finish_kernel() {
+        // The barrier orders every warp's stores before the signalling lanes; their release at system
+        // scope is cumulative over it (the pattern of a grid-wide barrier: bar.sync, then one fence + atomic).
+        __syncthreads();
+        if (threadIdx.x < peers.world) red_release_sys_add(pick(peers.done, threadIdx.x), 1u);
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            if (!counter_wait_bounded(pick(peers.done, peers.rank), launch_no * peers.world * gridDim.x)) atomicExch(&g_staged_status, 9);
+            *peers.launches = launch_no;
+            __threadfence();
+        }
+    }
 };
 
 // ---- Huffman: folded pair table ---------------------------------------------------------------------
@@ -495,6 +607,7 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     Sink sink = sink_proto;
     // Everything above read weights only.  X (and Y) belong to the previous kernel in the stream.
     pdl_wait();
+    sink.after_wait(lane);
     sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
     if (prepared == nullptr) {
         load_tables(tab, targs, threadIdx.x, blockDim.x);
@@ -605,6 +718,7 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         cur = nxt;
         slot ^= 1;
     }
+    sink.finish_kernel();
     BHI_TRACE_POINT(7);
 }
 
@@ -704,6 +818,46 @@ static int staged_gemv(const Layer &L, const typename Codec::Args &targs, const 
         case 6: return staged_gemv_b<Codec, 6>(L, targs, prepared, X, Y, st);
         case 7: return staged_gemv_b<Codec, 7>(L, targs, prepared, X, Y, st);
         case 8: return staged_gemv_b<Codec, 8>(L, targs, prepared, X, Y, st);
+    }
+    return kStagedDeclined;
+}
+
+template <class Codec, int B>
+static int staged_exchange_b(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                             const PeerSet &peers, cudaStream_t st) {
+    constexpr int NW = B <= 2 ? 32 : 16;
+    const int64_t K = static_cast<int64_t>(L.S) * L.Nc;
+    const int64_t x_need = ((static_cast<int64_t>(B) * K * 2 + 255) / 256) * 256;
+    auto fill = [&](auto &sink) {
+        sink.x = reinterpret_cast<const uint32_t *>(X);
+        sink.row_pairs = K >> 1;
+        sink.row_blocks = static_cast<int>(K >> 7);
+        sink.Y = nullptr;
+        sink.M = L.M;
+        sink.peers = peers;
+    };
+    if (x_need <= kXStageMax) {
+        ExchangeSink<B, true> sink{};
+        fill(sink);
+        return staged_launch<Codec, ExchangeSink<B, true>, NW>(L, targs, prepared, sink, static_cast<uint32_t>(x_need), st);
+    }
+    ExchangeSink<B, false> sink{};
+    fill(sink);
+    return staged_launch<Codec, ExchangeSink<B, false>, NW>(L, targs, prepared, sink, 0u, st);
+}
+
+template <class Codec>
+static int staged_exchange(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
+                           const PeerSet &peers, int B, cudaStream_t st) {
+    switch (B) {
+        case 1: return staged_exchange_b<Codec, 1>(L, targs, prepared, X, peers, st);
+        case 2: return staged_exchange_b<Codec, 2>(L, targs, prepared, X, peers, st);
+        case 3: return staged_exchange_b<Codec, 3>(L, targs, prepared, X, peers, st);
+        case 4: return staged_exchange_b<Codec, 4>(L, targs, prepared, X, peers, st);
+        case 5: return staged_exchange_b<Codec, 5>(L, targs, prepared, X, peers, st);
+        case 6: return staged_exchange_b<Codec, 6>(L, targs, prepared, X, peers, st);
+        case 7: return staged_exchange_b<Codec, 7>(L, targs, prepared, X, peers, st);
+        case 8: return staged_exchange_b<Codec, 8>(L, targs, prepared, X, peers, st);
     }
     return kStagedDeclined;
 }

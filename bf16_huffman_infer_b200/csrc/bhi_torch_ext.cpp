@@ -239,6 +239,71 @@ void boxed_linear_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
                               static_cast<int>(B), stream_of(rem)));
 }
 
+// Fills the C descriptor from a CPU int64 tensor [3 * world + 1]: y pointers, ready pointers, done
+// pointers (one per rank each), then the local launch counter.
+bhi_exchange_t exchange_of(const Tensor &peers, int64_t rank, int64_t row_base, int64_t m_total) {
+    STD_TORCH_CHECK(!peers.is_cuda() && peers.scalar_type() == ScalarType::Long && peers.is_contiguous(),
+                    "peers must be a contiguous CPU int64 tensor");
+    const int64_t n = peers.numel();
+    STD_TORCH_CHECK(n >= 4 && (n - 1) % 3 == 0 && (n - 1) / 3 <= BHI_MAX_PEERS, "peers must hold 3 * world + 1 pointers");
+    const int world = static_cast<int>((n - 1) / 3);
+    const int64_t *v = static_cast<const int64_t *>(peers.data_ptr());
+    bhi_exchange_t ex = {};
+    ex.world = world;
+    ex.rank = static_cast<int>(rank);
+    ex.row_base = static_cast<int>(row_base);
+    ex.M_total = static_cast<int>(m_total);
+    for (int r = 0; r < world; r++) {
+        ex.y[r] = reinterpret_cast<uint16_t *>(v[r]);
+        ex.ready[r] = reinterpret_cast<uint32_t *>(v[world + r]);
+        ex.done[r] = reinterpret_cast<uint32_t *>(v[2 * world + r]);
+    }
+    ex.launches = reinterpret_cast<uint32_t *>(v[3 * world]);
+    return ex;
+}
+
+// gemv_bf16_huffman_exchange(A_rem, A_exp, X, offsets, prepared, peers, rank, row_base, m_total) -> ()
+void boxed_gemv_bf16_huffman_exchange(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), off = arg(stack, 3), blob = arg(stack, 4),
+           peers = arg(stack, 5);
+    LayerView v = layer_of(rem, exp, off);
+    want(X, ScalarType::BFloat16, "X");
+    want(blob, ScalarType::Byte, "prepared");
+    same_device(rem, X, "X");
+    same_device(rem, blob, "prepared");
+    STD_TORCH_CHECK(blob.numel() == bhi_huffman_prepared_bytes(), "prepared has the wrong size");
+    const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
+    STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
+    const int64_t B = X.numel() / K;
+    STD_TORCH_CHECK(B <= BHI_MAX_BATCH, "batch_size <= 8");
+    const bhi_exchange_t ex = exchange_of(peers, iarg(stack, 6), iarg(stack, 7), iarg(stack, 8));
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_gemv_bf16_huffman_exchange(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
+                                         ptr<const int32_t>(off), ptr<const uint8_t>(blob), v.S, v.M, v.Nc,
+                                         static_cast<int>(B), &ex, stream_of(rem)));
+}
+
+// gemv_bf16_ans_exchange(A_rem, A_exp, X, offsets, LUT, peers, rank, row_base, m_total) -> ()
+void boxed_gemv_bf16_ans_exchange(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), off = arg(stack, 3), lut = arg(stack, 4),
+           peers = arg(stack, 5);
+    LayerView v = layer_of(rem, exp, off);
+    want(X, ScalarType::BFloat16, "X");
+    want(lut, ScalarType::Int, "LUT");
+    same_device(rem, X, "X");
+    same_device(rem, lut, "LUT");
+    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
+    STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
+    const int64_t B = X.numel() / K;
+    STD_TORCH_CHECK(B <= BHI_MAX_BATCH, "batch_size <= 8");
+    const bhi_exchange_t ex = exchange_of(peers, iarg(stack, 6), iarg(stack, 7), iarg(stack, 8));
+    torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
+    check(bhi_gemv_bf16_ans_exchange(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
+                                     ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc, static_cast<int>(B),
+                                     &ex, stream_of(rem)));
+}
+
 // ans_decode(A_rem, A_exp, Y(a!), offsets, LUT) -> ()
 void boxed_ans_decode(StableIValue *stack, uint64_t, uint64_t) {
     Tensor rem = arg(stack, 0), exp = arg(stack, 1), Y = arg(stack, 2), off = arg(stack, 3), lut = arg(stack, 4);
@@ -400,6 +465,8 @@ STABLE_TORCH_LIBRARY(BHI_TORCH_NAMESPACE, m) {
     m.def("huffman_decode_prepared(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("linear_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("linear_bf16_ans(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()");
+    m.def("gemv_bf16_huffman_exchange(Tensor A_rem, Tensor A_exp, Tensor X, Tensor offsets, Tensor prepared, Tensor peers, int rank, int row_base, int m_total) -> ()");
+    m.def("gemv_bf16_ans_exchange(Tensor A_rem, Tensor A_exp, Tensor X, Tensor offsets, Tensor LUT, Tensor peers, int rank, int row_base, int m_total) -> ()");
     m.def("set_launch_overlap(int on) -> int");
     // whole-layer encoder
     m.def("huffman_size_pass(Tensor W, int split_k, Tensor code_lengths, Tensor(a!) words_per_row) -> ()");
@@ -424,6 +491,8 @@ STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CUDA, m) {
     m.impl("huffman_decode_prepared", &boxed_huffman_decode_prepared);
     m.impl("linear_bf16_huffman_prepared", &boxed_linear_bf16_huffman_prepared);
     m.impl("linear_bf16_ans", &boxed_linear_bf16_ans);
+    m.impl("gemv_bf16_huffman_exchange", &boxed_gemv_bf16_huffman_exchange);
+    m.impl("gemv_bf16_ans_exchange", &boxed_gemv_bf16_ans_exchange);
     m.impl("huffman_size_pass", &boxed_huffman_size_pass);
     m.impl("huffman_emit_pass", &boxed_huffman_emit_pass);
     m.impl("ans_size_pass", &boxed_ans_size_pass);

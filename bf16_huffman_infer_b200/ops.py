@@ -84,6 +84,19 @@ def linear_bf16_ans(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tensor, offsets:
     _ops.linear_bf16_ans.default(A_rem, A_exp, X, Y, offsets, LUT)
 
 
+def gemv_bf16_huffman_exchange(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, prepared: Tensor,
+                               peers: Tensor, rank: int, row_base: int, m_total: int) -> None:
+    """Row-sharded fused GEMV that stores its results into every rank's output buffer (no reference
+    counterpart).  ``peers``: CPU int64 ``[3 * world + 1]`` = output, ready-counter and done-counter
+    pointers of every rank, then the local launch counter."""
+    _ops.gemv_bf16_huffman_exchange.default(A_rem, A_exp, X, offsets, prepared, peers, rank, row_base, m_total)
+
+
+def gemv_bf16_ans_exchange(A_rem: Tensor, A_exp: Tensor, X: Tensor, offsets: Tensor, LUT: Tensor,
+                           peers: Tensor, rank: int, row_base: int, m_total: int) -> None:
+    _ops.gemv_bf16_ans_exchange.default(A_rem, A_exp, X, offsets, LUT, peers, rank, row_base, m_total)
+
+
 def huffman_decode_prepared(A_rem: Tensor, A_exp: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
     _ops.huffman_decode_prepared.default(A_rem, A_exp, Y, offsets, prepared)
 

@@ -33,6 +33,7 @@ extern "C" {
 #define BHI_ERR_LIMIT 3    /* a size beyond a documented fixed limit */
 
 #define BHI_MAX_BATCH 8            /* rows of X the fused GEMV accepts */
+#define BHI_MAX_PEERS 8            /* ranks one exchange entry point can serve */
 #define BHI_MAX_LINEAR_BATCH 128   /* rows of X the fused tensor-core product accepts */
 #define BHI_ANS_PRECISION 8
 
@@ -56,9 +57,11 @@ int bhi_set_kernel_path(int path);
  * still in flight on the same stream).  Returns the previous value. */
 int bhi_set_launch_overlap(int on);
 
-/* Reads and clears the device-side status word of the current device (0 = no incident; 1 = a
- * bounded wait for a bulk copy expired inside a staged kernel and the affected record was
- * skipped).  Synchronises the device; meant for tests and post-mortems, not for the launch path. */
+/* Reads and clears the device-side status word of the current device.  0 = no incident; otherwise
+ * the last bounded wait that ran out inside a kernel: 1 a record's bulk copy (the record was
+ * skipped), 2 the prepared-table copy, 3-7 the tensor-core path's stage / accumulator barriers,
+ * 8 peers not ready and 9 peers not done in an exchange kernel.  The kernels always run to their
+ * end.  Synchronises the device; meant for tests and post-mortems, not for the launch path. */
 int bhi_debug_status(int *status_out);
 
 /* Y[b, m] = sum_c X[b, c] * W[m, c] computed straight from the Huffman-coded weight.
@@ -126,6 +129,36 @@ int bhi_linear_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp
 int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
                         const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
                         int split_k, int M, int Nc, int batch, void *stream);
+
+/* ---- row-sharded GEMV with the all-gather in its epilogue --------------------------------------
+ * For a weight whose output rows are split over `world` GPUs of one node (one process per GPU):
+ * this rank holds rows [row_base, row_base + M) of an [M_total, K] weight and computes
+ * Y[b, row_base + m]; every rank needs all of Y afterwards.  These entry points store each result
+ * straight into the Y buffer of every rank (y[r], peer-mapped device pointers, e.g. from CUDA IPC
+ * or torch symmetric memory) and return only when, in stream order, all ranks' rows have arrived
+ * in y[rank]: no collective call follows.  All ranks must call them for the same layer in the
+ * same order.  No counterpart in the reference (single GPU).
+ *
+ * ready[r], done[r]: one u32 word per rank for THIS layer, in peer-mapped memory, zero before the
+ * first call and never touched by the caller afterwards; launches: one u32 word in local memory,
+ * zero before the first call.  The kernel signals the peers that y may be overwritten only after
+ * everything earlier in `stream` has finished, so consumers of Y must be ordered on the same
+ * stream.  Waits on peers are bounded (one second each); if one runs out the status word is set
+ * (bhi_debug_status) and Y is incomplete.  batch <= BHI_MAX_BATCH, world <= BHI_MAX_PEERS. */
+typedef struct {
+    int world, rank;
+    int row_base, M_total;
+    uint16_t *y[BHI_MAX_PEERS];       /* Y [batch, M_total] bf16 of every rank */
+    uint32_t *ready[BHI_MAX_PEERS];
+    uint32_t *done[BHI_MAX_PEERS];
+    uint32_t *launches;
+} bhi_exchange_t;
+int bhi_gemv_bf16_huffman_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                   const uint16_t *X, const int32_t *offsets, const uint8_t *prepared,
+                                   int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
+int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT,
+                               int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
 
 /* Per-stream Huffman code emission as ASCII '0'/'1' characters.
  *   data u8 [streams, n]; LUT u8 [256, 32] code strings (root first, NUL padded);
