@@ -137,6 +137,34 @@ static int run_exchange(const Layer &L, const typename Codec::Args &targs, const
     return rc == kStagedDeclined ? fail(BHI_ERR_ARG, "shape not supported by the exchange kernel") : rc;
 }
 
+// ---- exchange counters kept inside the library (bhi_gemv_bf16_huffman_exchange_static) --------------
+// One 256-byte entry per layer slot: ready counter at word 0, done counter at word 32, launch counter at
+// word 48.  File-scope device memory: nothing is allocated; the address is looked up once per device.
+constexpr int kStaticWordsPerLayer = 64;
+static __device__ __align__(256) uint32_t g_static_exchange[BHI_STATIC_EXCHANGE_LAYERS * kStaticWordsPerLayer];
+
+static int static_exchange_base(cudaStream_t st, uint32_t **base_out) {
+    static std::mutex mu;
+    static uint32_t *base[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(BHI_ERR_CUDA, "cudaGetDevice failed");
+    std::lock_guard<std::mutex> lock(mu);
+    if (base[dev] == nullptr) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaError_t e = cudaStreamIsCapturing(st, &cap);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaStreamIsCapturing");
+        BHI_REQUIRE(cap == cudaStreamCaptureStatusNone, "the first call on a device must be made outside stream capture");
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_exchange);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress");
+        e = cudaMemsetAsync(p, 0, sizeof(uint32_t) * BHI_STATIC_EXCHANGE_LAYERS * kStaticWordsPerLayer, st);   // counters start at zero
+        if (e != cudaSuccess) return cuda_fail(e, "clearing the exchange counters");
+        base[dev] = static_cast<uint32_t *>(p);
+    }
+    *base_out = base[dev];
+    return BHI_OK;
+}
+
 static int check_enc(const void *W, int M, int K, int S) {
     BHI_REQUIRE(W, "null weight");
     BHI_REQUIRE(M >= 1 && K >= 128 && S >= 1 && K % S == 0, "bad shape");
@@ -281,6 +309,33 @@ int bhi_gemv_bf16_huffman_exchange(const uint8_t *A_rem, const uint32_t *A_exp, 
     const uint8_t *ex = prepared + kPairEntries * 4;
     HuffArgs t{ex, ex + 256, ex + 512, ex + 768, ex + 1024};
     return run_exchange<HuffCodec>(L, t, prepared, X, batch, exchange, static_cast<cudaStream_t>(stream));
+}
+
+int bhi_gemv_bf16_huffman_exchange_static(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                          const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                          const uint8_t *prepared, int split_k, int M, int Nc, int batch,
+                                          int layer_slot, void *stream) {
+    if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
+    BHI_REQUIRE(prepared && aligned(prepared, 16), "null or unaligned prepared tables");
+    BHI_REQUIRE(Y && aligned(Y, 2), "null or unaligned output");
+    if (layer_slot < 0 || layer_slot >= BHI_STATIC_EXCHANGE_LAYERS)
+        return fail(BHI_ERR_LIMIT, "layer_slot outside [0, BHI_STATIC_EXCHANGE_LAYERS)");
+    uint32_t *words = nullptr;
+    if (int rc = static_exchange_base(static_cast<cudaStream_t>(stream), &words)) return rc;
+    words += static_cast<size_t>(layer_slot) * kStaticWordsPerLayer;
+    bhi_exchange_t ex = {};
+    ex.world = 1;
+    ex.rank = 0;
+    ex.row_base = 0;
+    ex.M_total = M;
+    ex.y[0] = Y;
+    ex.ready[0] = words;
+    ex.done[0] = words + 32;
+    ex.launches = words + 48;
+    Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
+    const uint8_t *t = prepared + kPairEntries * 4;
+    HuffArgs args{t, t + 256, t + 512, t + 768, t + 1024};
+    return run_exchange<HuffCodec>(L, args, prepared, X, batch, &ex, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,

@@ -160,6 +160,21 @@ int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int6
                                const uint16_t *X, const int32_t *offsets, const uint32_t *LUT,
                                int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
 
+/* Single-GPU form of bhi_gemv_bf16_huffman_exchange whose counter words live inside the library
+ * (no counterpart in the reference).  Y [batch, M] is an ordinary output buffer; the three counter
+ * words of the exchange protocol (ready, done, launches) are taken from a file-scope device array of
+ * BHI_STATIC_EXCHANGE_LAYERS entries of 256 bytes (256 KB per device), entry `layer_slot`; slots
+ * outside [0, BHI_STATIC_EXCHANGE_LAYERS) are rejected with BHI_ERR_LIMIT.  Nothing is allocated:
+ * the array's address is looked up once per device and the array is cleared then (the first call on
+ * a device must therefore not be made while `stream` is being captured; it returns BHI_ERR_ARG if it
+ * is).  Calls that use the same slot and may overlap in time (different streams, or threads) race on
+ * its counters and must be serialised by the caller; different slots are independent. */
+#define BHI_STATIC_EXCHANGE_LAYERS 1024
+int bhi_gemv_bf16_huffman_exchange_static(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
+                                          const uint16_t *X, uint16_t *Y, const int32_t *offsets,
+                                          const uint8_t *prepared, int split_k, int M, int Nc, int batch,
+                                          int layer_slot, void *stream);
+
 /* Per-stream Huffman code emission as ASCII '0'/'1' characters.
  *   data u8 [streams, n]; LUT u8 [256, 32] code strings (root first, NUL padded);
  *   output u8 [streams, 32*n] (caller pre-fills with '0'); output_lengths i32 [streams] = bits.
