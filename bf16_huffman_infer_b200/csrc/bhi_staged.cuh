@@ -55,7 +55,8 @@ constexpr int kHeaderBytes = kLutBytes + kExactBytes + kCtrlBytes;
 constexpr int kSlackBytes = 2048;              // readable space above the last ring
 constexpr int kSmemMax = 227 * 1024;
 constexpr int kRingMax = 8192;
-constexpr int kXStageMax = 32 * 1024;          // X is staged in shared memory up to this many bytes
+constexpr int kXStageMax = 32 * 1024;          // X is staged in shared memory up to this many bytes (32 warps)
+constexpr int kXStageMax16 = 64 * 1024;        // ... with 16 warps, whose rings need half the room
 constexpr int kGroup = 8;                      // blocks per rem prefetch group (8 measured 2 % faster than 4)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -787,7 +788,7 @@ static int staged_gemv_b(const Layer &L, const typename Codec::Args &targs, cons
     constexpr int NW = B <= 2 ? 32 : 16;
     const int64_t K = static_cast<int64_t>(L.S) * L.Nc;
     const int64_t x_need = ((static_cast<int64_t>(B) * K * 2 + 255) / 256) * 256;
-    if (x_need <= kXStageMax) {
+    if (x_need <= (NW == 16 ? kXStageMax16 : kXStageMax)) {
         GemvSink<B, true> sink{};
         sink.x = reinterpret_cast<const uint32_t *>(X);
         sink.row_pairs = K >> 1;
@@ -836,7 +837,7 @@ static int staged_exchange_b(const Layer &L, const typename Codec::Args &targs, 
         sink.M = L.M;
         sink.peers = peers;
     };
-    if (x_need <= kXStageMax) {
+    if (x_need <= (NW == 16 ? kXStageMax16 : kXStageMax)) {
         ExchangeSink<B, true> sink{};
         fill(sink);
         return staged_launch<Codec, ExchangeSink<B, true>, NW>(L, targs, prepared, sink, static_cast<uint32_t>(x_need), st);
