@@ -1,8 +1,8 @@
 """Generate ``tests/golden/ref_tables.json`` and ``tests/golden/ref_streams.json``.
 
-Run in a container where the reference project is mounted (default ``/root/reference``):
+Run where the reference project's sources are available:
 
-    python tests/golden/make_golden_cpu.py [/path/to/reference]
+    python tests/golden/make_golden_cpu.py /path/to/reference
 
 It imports the reference's pure-Python modules ``bf16_huffman_infer/huffman.py`` and
 ``bf16_huffman_infer/ans.py`` by path (they need no GPU) and records
@@ -23,7 +23,7 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BHI_REFERENCE_DIR", "reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

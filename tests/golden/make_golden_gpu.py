@@ -3,8 +3,7 @@
 Needs the reference installed at ``baseline/_ref`` (``pip install --target baseline/_ref`` of the
 reference project, built for sm_100a) and a GPU:
 
-    python tests/golden/make_golden_gpu.py            # writes tests/golden/ref_layout_*.npz
-                                                      # (and copies to gpurun_out/ when that exists)
+    python tests/golden/make_golden_gpu.py [extra_output_dir]      # writes tests/golden/ref_layout_*.npz
 
 For a few small seeded layers it runs the reference's own ``HuffmanWeight.compress`` /
 ``ANSWeight.compress`` (or ``compress_split_n`` to force a K-split), its ``get_weight`` decode and its
@@ -41,9 +40,7 @@ def weight(M, K, seed, std):
 
 
 def main():
-    out_dirs = [HERE]
-    if os.path.isdir(os.path.join(ROOT, "gpurun_out")):
-        out_dirs.append(os.path.join(ROOT, "gpurun_out"))
+    out_dirs = [HERE] + [d for d in sys.argv[1:2] if os.path.isdir(d)]      # a second copy, e.g. on a scratch volume
     for name, algo, M, K, split, seed in CASES:
         std = 1.0 if "std1" in name else 0.02
         W = weight(M, K, seed, std)

@@ -96,11 +96,10 @@ def test_two_ranks_played_in_turn(abi, algo, M, K, S, B):
             _launch(abi, algo, shards[r], x, ex)
             torch.cuda.synchronize()
             if r == 0:
-                # rank 1 really signals below: take the credit back out of rank 0's words first,
-                # so that they end the round at exactly world * launch number (and world * grid * ...)
+                # rank 1 really signals below: take the credit back out of rank 0's words first, so that
+                # they end this call at exactly world * launch number (and world * grid * launch number)
                 counters[r, 0, 0] -= 1
                 counters[r, 1, 0] -= grid
-                # rank 1's own words still miss rank 0's arrivals of this round? no: rank 0 added them above
         assert _status(abi) == 0
         for q in range(world):
             got = y[q][:B].float().cpu().numpy()
