@@ -38,6 +38,7 @@
 
 #include <mutex>
 #include <type_traits>
+#include <unordered_map>
 
 #include "bhi_common.cuh"
 
@@ -57,6 +58,7 @@ constexpr int kSmemMax = 227 * 1024;
 constexpr int kRingMax = 8192;
 constexpr int kXStageMax = 32 * 1024;          // X is staged in shared memory up to this many bytes (32 warps)
 constexpr int kXStageMax16 = 64 * 1024;        // ... with 16 warps, whose rings need half the room
+constexpr int kPartMax = 16 * 1024;             // most shared memory spent on staged results
 constexpr int kGroup = 8;                      // blocks per rem prefetch group (8 measured 2 % faster than 4)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -202,6 +204,28 @@ struct GemvSink {
             acc[b] = make_float2(0.f, 0.f);
         }
     }
+    // staged results: part[(b * rows + r) * slots + slot]
+    static constexpr int kBatch = B;
+    static constexpr bool kStagesResults = false;      // only when the launch asks for split work
+    __device__ __forceinline__ void finish_part(float *part, int r, int slot, int rows, int slots, int lane) {
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            const float v = warp_sum(acc[b].x + acc[b].y);
+            if (lane == 0) part[(b * rows + r) * slots + slot] = v;
+            acc[b] = make_float2(0.f, 0.f);
+        }
+    }
+    static __device__ __forceinline__ float part_sum(const float *part, int i, int slots) {
+        float v = part[i * slots];
+        for (int s = 1; s < slots; s++) v += part[i * slots + s];
+        return v;
+    }
+    __device__ __forceinline__ void combine(const float *part, int row_lo, int rows, int slots, int) {
+        for (int i = threadIdx.x; i < B * rows; i += blockDim.x) {
+            const int b = i / rows, r = i - b * rows;
+            Y[static_cast<int64_t>(b) * M + row_lo + r] = f32_to_bf16_rn(part_sum(part, i, slots));
+        }
+    }
 };
 
 struct DenseSink {
@@ -218,6 +242,10 @@ struct DenseSink {
         row[gblk * 64 + 32] = w1;
     }
     __device__ __forceinline__ void finish_row(int, int) {}
+    static constexpr int kBatch = 0;
+    static constexpr bool kStagesResults = false;
+    __device__ __forceinline__ void finish_part(float *, int, int, int, int, int) {}
+    __device__ __forceinline__ void combine(const float *, int, int, int, int) {}
 };
 
 // ---- row-sharded GEMV whose epilogue is the all-gather ------------------------------------------------
@@ -313,6 +341,20 @@ struct ExchangeSink : GemvSink<B, kXS> {
             const float v = warp_sum(Base::acc[b].x + Base::acc[b].y);          // every lane holds the sum
             if (lane < peers.world) dst[static_cast<int64_t>(b) * peers.m_total + peers.row_base + m] = f32_to_bf16_rn(v);
             Base::acc[b] = make_float2(0.f, 0.f);
+        }
+    }
+    // Results staged in shared memory leave for every rank at the end, consecutive threads writing
+    // consecutive rows (coalesced peer stores instead of one 2-byte store per row and rank).
+    static constexpr bool kStagesResults = true;
+    __device__ __forceinline__ void combine(const float *part, int row_lo, int rows, int slots, int lane) {
+        if (!counter_wait_bounded(pick(peers.ready, peers.rank), launch_no * peers.world) && lane == 0) atomicExch(&g_staged_status, 8);
+        for (int i = threadIdx.x; i < B * rows; i += blockDim.x) {
+            const int b = i / rows, r = i - b * rows;
+            const uint16_t v = f32_to_bf16_rn(Base::part_sum(part, i, slots));
+            const int64_t at = static_cast<int64_t>(b) * peers.m_total + peers.row_base + row_lo + r;
+#pragma unroll
+            for (int q = 0; q < kMaxPeers; q++)
+                if (q < peers.world) peers.y[q][at] = v;
         }
     }
     __device__ __forceinline__ void finish_kernel() {
@@ -516,10 +558,14 @@ struct Unit {
     bool valid, staged;
 };
 
-template <class Codec, class Sink, int NW>
+// kPart: results are staged in shared memory (and work may be split by record); a compile-time switch so
+// that the plain instantiation carries none of it.
+template <class Codec, class Sink, int NW, bool kPart>
 __global__ void __launch_bounds__(NW * 32, 1)
 staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink sink_proto, uint32_t x_bytes,
-              uint32_t ring_bytes, Consts k) {
+              uint32_t ring_bytes, Consts k, uint32_t part_bytes_arg, int split_arg) {
+    const uint32_t part_bytes = kPart ? part_bytes_arg : 0u;
+    const bool split = kPart && split_arg != 0;
     extern __shared__ __align__(256) uint8_t smem[];
     using Tables = typename Codec::Tables;
     using Dec = typename StagedOf<Codec>::type;
@@ -534,7 +580,12 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     const int warp = threadIdx.x >> 5;
     const uint32_t lane4 = 4u * lane;
     const uint32_t copy_off = 4u * (lane & (kCopies - 1));            // this lane's copy of the fast table
-    const uint32_t ring = kHeaderBytes + x_bytes + warp * ring_bytes;     // byte offset in smem, 256-aligned
+    // Optional result staging (part_bytes > 0): dot products go to part[b][row][slot] in shared memory and
+    // are written out by the whole CTA at the end.  With `split` a unit of work is one (row, chunk) record
+    // instead of a whole row - for layers with fewer rows than warps - and slot = chunk; the chunks of a row
+    // are summed in chunk order at the end, so the result does not depend on which warp took which.
+    float *part = reinterpret_cast<float *>(smem + kHeaderBytes + x_bytes);
+    const uint32_t ring = kHeaderBytes + x_bytes + part_bytes + warp * ring_bytes;     // byte offset in smem, 256-aligned
     const uint32_t smem_base = smem_addr(smem);
     const uint32_t bar0 = smem_addr(&bars[2 * warp]);                      // slot s uses the barrier at bar0 + 8*s
 
@@ -542,12 +593,14 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     const int row_hi = static_cast<int>(static_cast<int64_t>(L.M) * (blockIdx.x + 1) / gridDim.x);
     const int64_t nrec = static_cast<int64_t>(L.S) * L.M;
     const int nblk = L.Nc >> 7;
+    const int rows_cta = row_hi - row_lo;
+    const int slots = split ? L.S : 1;             // partial sums kept per row when results are staged
 
     BHI_TRACE_POINT(0);
     pdl_launch_dependents();
     // The first row of every warp is fixed (row_lo + warp), so its sign/mantissa row can be
     // requested from HBM before anything else is known; later rows come from the shared counter.
-    if (lane == 0 && row_lo + warp < row_hi)
+    if (lane == 0 && !split && row_lo + warp < row_hi)
         prefetch_l2(L.rem + static_cast<int64_t>(row_lo + warp) * L.Nc, static_cast<uint32_t>(L.Nc));
     if (threadIdx.x == 0) {
         *row_counter = NW;
@@ -567,10 +620,10 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         bulk_copy_g2s(smem_base + kLutBytes - kPairEntries * 4, prepared, kPreparedBytes, table_bar);
     }
 
-    auto next_row = [&]() -> int {
+    auto next_index = [&]() -> int {               // next row (or, with `split`, next record) of this CTA
         int v = 0;
         if (lane == 0) v = atomicAdd(row_counter, 1);
-        return row_lo + __shfl_sync(0xFFFFFFFFu, v, 0);
+        return __shfl_sync(0xFFFFFFFFu, v, 0);
     };
     auto describe = [&](int m, int k, Unit &u) {
         u.m = m;
@@ -596,12 +649,19 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     };
     auto rem_ptr = [&](const Unit &u) { return reinterpret_cast<const uint32_t *>(L.rem + u.rec * L.Nc) + lane; };
 
+    // index v of the CTA's work list -> unit: row row_lo + v, or record (row_lo + v / S, v % S)
+    auto unit_at = [&](int v, Unit &u) {
+        if (split) {
+            if (v < rows_cta * L.S) describe(row_lo + v / L.S, v % L.S, u);
+        } else if (row_lo + v < row_hi) {
+            describe(row_lo + v, 0, u);
+        }
+    };
+
     Unit cur, nxt;
     cur.valid = false;
-    if (row_lo + warp < row_hi) {
-        describe(row_lo + warp, 0, cur);
-        if (cur.staged) issue(cur, 0);
-    }
+    unit_at(warp, cur);
+    if (cur.valid && cur.staged) issue(cur, 0);
 
     BHI_TRACE_POINT(1);
     // tables and X: overlaps the first copy in flight
@@ -640,12 +700,8 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
 
     while (cur.valid) {
         nxt.valid = false;
-        if (cur.k + 1 < L.S) {
-            describe(cur.m, cur.k + 1, nxt);
-        } else {
-            const int m = next_row();
-            if (m < row_hi) describe(m, 0, nxt);
-        }
+        if (!split && cur.k + 1 < L.S) describe(cur.m, cur.k + 1, nxt);
+        else unit_at(next_index(), nxt);
         const bool early = nxt.valid && nxt.staged && (!cur.staged || cur.exp_bytes + nxt.exp_bytes <= ring_bytes);
         if (early) issue(nxt, slot ^ 1);
 
@@ -713,11 +769,19 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         }
         BHI_TRACE_POINT(have_first ? 6 : 4);
         have_first = next_first;
-        if (cur.k == L.S - 1) sink.finish_row(cur.m, lane);
+        if (kPart) {
+            if (split || cur.k == L.S - 1) sink.finish_part(part, cur.m - row_lo, split ? cur.k : 0, rows_cta, slots, lane);
+        } else if (cur.k == L.S - 1) {
+            sink.finish_row(cur.m, lane);
+        }
         __syncwarp();
         if (nxt.valid && nxt.staged && !early) issue(nxt, slot ^ 1);
         cur = nxt;
         slot ^= 1;
+    }
+    if (kPart) {
+        __syncthreads();
+        sink.combine(part, row_lo, rows_cta, slots, lane);
     }
     sink.finish_kernel();
     BHI_TRACE_POINT(7);
@@ -728,16 +792,19 @@ bool overlap_launches();     // process-wide switch, see bhi_set_launch_overlap
 
 template <class K>
 static int staged_prepare(K kernel) {
-    // Opt in to the large dynamic shared-memory carve-out once per device and kernel.
+    // Opt in to the large dynamic shared-memory carve-out once per device and kernel.  Keyed by the
+    // kernel's address: instantiations that differ only in a non-type argument share their pointer type.
     static std::mutex mu;
-    static bool done[64];
+    static std::unordered_map<const void *, uint64_t> done;      // kernel -> bit per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BHI_ERR_CUDA;
+    const void *key = reinterpret_cast<const void *>(kernel);
     std::lock_guard<std::mutex> lock(mu);
-    if (!done[dev]) {
+    uint64_t &bits = done[key];
+    if (!(bits >> dev & 1u)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
-        done[dev] = true;
+        bits |= 1ull << dev;
     }
     return BHI_OK;
 }
@@ -759,14 +826,27 @@ __global__ void __launch_bounds__(1024) huffman_prepare_kernel(HuffArgs targs, u
 template <class Codec, class Sink, int NW>
 static int staged_launch(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const Sink &sink,
                          uint32_t x_bytes, cudaStream_t st) {
-    auto kernel = staged_kernel<Codec, Sink, NW>;
-    if (int rc = staged_prepare(kernel)) return rc;
-    const uint32_t avail = kSmemMax - kHeaderBytes - kSlackBytes - x_bytes;
-    uint32_t ring_bytes = (avail / NW) & ~255u;
-    if (ring_bytes > kRingMax) ring_bytes = kRingMax;
-    const uint32_t smem_bytes = kHeaderBytes + x_bytes + NW * ring_bytes + kSlackBytes;
     int grid = sm_count();
     if (grid > L.M) grid = L.M;
+    // Work is split by (row, chunk) records when a CTA has fewer rows than warps and rows have several
+    // chunks; results are then (and for sinks that ask for it) staged in shared memory, if they fit.
+    const int rows_cta = (L.M + grid - 1) / grid;
+    // (measured: with more than half the warps holding a row of their own, whole rows are faster)
+    int split = (Sink::kBatch > 0 && L.S > 1 && 2 * rows_cta <= NW) ? 1 : 0;
+    uint32_t part_bytes = 0;
+    if (split || Sink::kStagesResults) {
+        part_bytes = ((static_cast<uint32_t>(Sink::kBatch) * rows_cta * (split ? L.S : 1) * 4u) + 255u) & ~255u;
+        if (part_bytes > kPartMax) {
+            part_bytes = 0;
+            split = 0;
+        }
+    }
+    auto kernel = part_bytes ? staged_kernel<Codec, Sink, NW, true> : staged_kernel<Codec, Sink, NW, false>;
+    if (int rc = staged_prepare(kernel)) return rc;
+    const uint32_t avail = kSmemMax - kHeaderBytes - kSlackBytes - x_bytes - part_bytes;
+    uint32_t ring_bytes = (avail / NW) & ~255u;
+    if (ring_bytes > kRingMax) ring_bytes = kRingMax;
+    const uint32_t smem_bytes = kHeaderBytes + x_bytes + part_bytes + NW * ring_bytes + kSlackBytes;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(NW * 32);
@@ -778,7 +858,7 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
     const Consts k{1u, 8u, 4u * kCopies, 65536u};
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes, k);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes, k, part_bytes, split);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
 }
 
