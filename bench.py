@@ -220,7 +220,18 @@ def build_stack(workload, algo, rank, world, dev, verify=True, exchange="peer"):
         meta.append(info)
         del W
     if arena is not None:
-        arena.commit()
+        # Peer-mapped memory needs every rank to succeed; if any cannot map it, all fall back to the all-gather.
+        import torch.distributed as dist
+        ok = torch.ones(1, device=dev)
+        try:
+            arena.commit()
+        except Exception as e:                                    # noqa: BLE001  (report and fall back)
+            print(f"[bench] rank {rank}: peer memory unavailable ({e}); using the NCCL all-gather", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            mods = [RowShardedLinear(m.local, m.out_features) for m in mods]
+            meta[0]["exchange_fallback"] = True
     return mods, meta
 
 
@@ -329,7 +340,7 @@ def ours(args, rank, world, dev):
             "setup_s": round(setup_s, 1),
             "exchange": ("none (one GPU)" if world == 1 else
                          "results stored into every rank's buffer by the kernel's epilogue (peer memory over NVLink)"
-                         if args.exchange == "peer" else "NCCL all-gather after every matrix"),
+                         if args.exchange == "peer" and not meta[0].get("exchange_fallback") else "NCCL all-gather after every matrix"),
         },
         "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(x_host.numel() * 2),
                 "d2h_bytes_per_step": int(y_host.numel() * 2)},
