@@ -1,7 +1,8 @@
 """Benchmark of the fused decode+GEMV hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload qwen3-8b|llama3-70b|tiny] [--algo huffman|ans|smallest] [--batch B]
+                    [--workload qwen3-8b+fused|qwen3-8b|llama3-70b[+fused]|tiny|layer:MxK|stack:NxMxK]
+                    [--algo huffman|ans|smallest] [--tables escape|reference] [--batch B] [--exchange peer|nccl]
 
 One "step" is one decode token's worth of the hot path: every compressed linear layer of a
 decoder of the named shape applied once, in model order, to a batch of B activation rows (B = 1
@@ -17,10 +18,15 @@ Printed JSON line (rank 0):
   roofline algorithmic compressed bytes per launch / average launch time of the fused kernel,
            against the measured HBM copy bandwidth of MEASURED_PEAKS.json;
   cpu_baseline  the CPU restatement of the reference's fused path (oracle/, all host threads) on a
-           bounded sample of the same workload.
-`--impl reference` times that CPU path alone and prints the same line shape.
-With N > 1 (launched under torchrun) every layer is sharded by output rows across the ranks and
-the slices are all-gathered over NCCL (strong scaling: the model is fixed).
+           bounded sample of the same workload;
+  reference_tables  (one GPU, Huffman) the same stack encoded with the reference's own table builder
+           instead of the escape-byte builder, timed the same way;
+  dense_bf16_torch  the uncompressed stack as torch nn.Linear layers on the same GPU.
+`--impl reference` times the CPU path alone and prints the same line shape.
+With N > 1 (launched under torchrun) every layer is sharded by output rows across the ranks; the
+slices are put together by the kernel's own epilogue (stores into every rank's buffer over NVLink,
+`--exchange peer`, the default) or by an NCCL all-gather (`--exchange nccl`).  Strong scaling: the
+model is fixed.
 """
 from __future__ import annotations
 

@@ -147,11 +147,31 @@ __device__ __forceinline__ float2 bf16x2_to_f32x2(uint32_t p) { return make_floa
 
 // ---- sinks: what happens to the two bf16x2 words a lane produces per 128-column block --------------
 // gblk = index of the 128-column block inside the full row (chunk * blocks_per_chunk + block).
+//
+// The multiply-accumulate runs on the warp-level tensor-core instruction (mma.sync m16n8k16, BF16 in,
+// FP32 accumulate) without any conversion or data movement: the two words w0, w1 a lane has just
+// rebuilt ARE its B fragment (k = the 16 columns its lane group holds, n = its lane group), and the
+// lane's own X pairs of the same columns are its A fragment (rows 0..7 = one batch row seen by the 8
+// lane groups, rows 8..15 = the next batch row).  D[g][g'] is then the dot product of group g's X
+// columns with group g''s W columns; only the diagonal g = g' is meaningful, and the sum of the 8
+// diagonal entries is the block's contribution to the row's dot product.  One instruction replaces
+// eight conversions and two packed FMAs per batch row; the seven off-diagonal products are waste the
+// tensor pipe has room for.
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <int B, bool kXS>
 struct GemvSink {
-    float2 acc[B];
+    static constexpr int kPairs = B / 2;       // batch rows handled two per instruction
+    static constexpr bool kOdd = (B & 1) != 0; // ... and a last one alone
+    float c[kPairs + (kOdd ? 1 : 0)][4];
     const uint32_t *x;      // X as bf16 pairs (global)
-    const uint2 *xs;        // X staged in shared memory: [b][gblk][lane] -> {pair at 2l, pair at 64+2l}
+    const uint4 *xq;        // staged: [pair][gblk][lane] -> {b: pair at 2l, b+1: pair at 2l, b: pair at 64+2l, b+1: pair at 64+2l}
+    const uint2 *xo;        // staged, last row of an odd batch: [gblk][lane] -> {pair at 2l, pair at 64+2l}
     int64_t row_pairs;      // K / 2
     int row_blocks;         // K / 128
     uint16_t *Y;
@@ -159,50 +179,81 @@ struct GemvSink {
 
     __device__ __forceinline__ void stage(uint8_t *x_region, int tid, int nthreads) {
         if (kXS) {
-            uint2 *dst = reinterpret_cast<uint2 *>(x_region);
-            const int total = B * row_blocks * 32;
-            for (int i = tid; i < total; i += nthreads) {
+            uint4 *dq = reinterpret_cast<uint4 *>(x_region);
+            const int per = row_blocks * 32;
+            for (int i = tid; i < kPairs * per; i += nthreads) {
                 const int l = i & 31, gb = i >> 5;
-                const int b = gb / row_blocks, g = gb - b * row_blocks;
-                const uint32_t *src = x + b * row_pairs + g * 64 + l;
-                dst[i] = make_uint2(__ldg(src), __ldg(src + 32));
+                const int p = gb / row_blocks, g = gb - p * row_blocks;
+                const uint32_t *s0 = x + (2 * p) * row_pairs + g * 64 + l;
+                const uint32_t *s1 = s0 + row_pairs;
+                dq[i] = make_uint4(__ldg(s0), __ldg(s1), __ldg(s0 + 32), __ldg(s1 + 32));
             }
-            xs = dst;
+            uint2 *dk = reinterpret_cast<uint2 *>(dq + kPairs * per);
+            if (kOdd) {
+                for (int i = tid; i < per; i += nthreads) {
+                    const uint32_t *s0 = x + (B - 1) * row_pairs + (i >> 5) * 64 + (i & 31);
+                    dk[i] = make_uint2(__ldg(s0), __ldg(s0 + 32));
+                }
+            }
+            xq = dq;
+            xo = dk;
         }
+    }
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int p = 0; p < kPairs + (kOdd ? 1 : 0); p++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) c[p][j] = 0.f;
     }
     __device__ __forceinline__ void reset(int lane) {
         x += lane;
-        xs += lane;
-#pragma unroll
-        for (int b = 0; b < B; b++) acc[b] = make_float2(0.f, 0.f);
+        xq += lane;
+        xo += lane;
+        clear();
     }
     __device__ __forceinline__ void begin_record(int) {}
     __device__ __forceinline__ void after_wait(int) {}        // right after the wait for the previous kernel
     __device__ __forceinline__ void finish_kernel() {}        // last thing the kernel does
-    __device__ __forceinline__ void put(const Consts &k, int gblk, uint32_t w0, uint32_t w1) {
-        // low half: w << 16 as a multiply (FMA pipe); high half: one mask
-        const float2 f0 = make_float2(__uint_as_float(w0 * k.shift16), bf16hi_to_f32(w0));
-        const float2 f1 = make_float2(__uint_as_float(w1 * k.shift16), bf16hi_to_f32(w1));
+    __device__ __forceinline__ void put(const Consts &, int gblk, uint32_t w0, uint32_t w1) {
 #pragma unroll
-        for (int b = 0; b < B; b++) {
-            uint2 xv;
+        for (int p = 0; p < kPairs; p++) {
+            uint4 q;
             if (kXS) {
-                xv = xs[(b * row_blocks + gblk) * 32];
+                q = xq[(p * row_blocks + gblk) * 32];
             } else {
-                const uint32_t *src = x + b * row_pairs + gblk * 64;
-                xv = make_uint2(__ldg(src), __ldg(src + 32));
+                const uint32_t *s0 = x + (2 * p) * row_pairs + gblk * 64;
+                const uint32_t *s1 = s0 + row_pairs;
+                q = make_uint4(__ldg(s0), __ldg(s1), __ldg(s0 + 32), __ldg(s1 + 32));
             }
-            acc[b] = ffma2(f0, make_float2(__uint_as_float(xv.x * k.shift16), bf16hi_to_f32(xv.x)), acc[b]);
-            acc[b] = ffma2(f1, make_float2(__uint_as_float(xv.y * k.shift16), bf16hi_to_f32(xv.y)), acc[b]);
+            mma_bf16_16x8x16(c[p], q.x, q.y, q.z, q.w, w0, w1);
         }
+        if (kOdd) {
+            uint2 q;
+            if (kXS) {
+                q = xo[gblk * 32];
+            } else {
+                const uint32_t *s0 = x + (B - 1) * row_pairs + gblk * 64;
+                q = make_uint2(__ldg(s0), __ldg(s0 + 32));
+            }
+            mma_bf16_16x8x16(c[kPairs], q.x, 0u, q.y, 0u, w0, w1);
+        }
+    }
+    // The dot product of batch row b so far: the diagonal entries of its accumulator tile live in the lanes
+    // whose column pair contains their lane group's index; everything else in the tile is discarded.
+    __device__ __forceinline__ float row_value(int b, int lane) const {
+        const bool holds = (lane & 3) == (lane >> 3);
+        const bool second = ((lane >> 2) & 1) != 0;
+        const float *t = c[b >> 1];
+        const float lo = second ? t[1] : t[0], hi = second ? t[3] : t[2];
+        return warp_sum(holds ? ((b & 1) ? hi : lo) : 0.f);
     }
     __device__ __forceinline__ void finish_row(int m, int lane) {
 #pragma unroll
         for (int b = 0; b < B; b++) {
-            const float v = warp_sum(acc[b].x + acc[b].y);
+            const float v = row_value(b, lane);
             if (lane == 0) Y[static_cast<int64_t>(b) * M + m] = f32_to_bf16_rn(v);
-            acc[b] = make_float2(0.f, 0.f);
         }
+        clear();
     }
     // staged results: part[(b * rows + r) * slots + slot]
     static constexpr int kBatch = B;
@@ -210,10 +261,10 @@ struct GemvSink {
     __device__ __forceinline__ void finish_part(float *part, int r, int slot, int rows, int slots, int lane) {
 #pragma unroll
         for (int b = 0; b < B; b++) {
-            const float v = warp_sum(acc[b].x + acc[b].y);
+            const float v = row_value(b, lane);
             if (lane == 0) part[(b * rows + r) * slots + slot] = v;
-            acc[b] = make_float2(0.f, 0.f);
         }
+        clear();
     }
     static __device__ __forceinline__ float part_sum(const float *part, int i, int slots) {
         float v = part[i * slots];
@@ -338,10 +389,10 @@ struct ExchangeSink : GemvSink<B, kXS> {
         }
 #pragma unroll
         for (int b = 0; b < B; b++) {
-            const float v = warp_sum(Base::acc[b].x + Base::acc[b].y);          // every lane holds the sum
+            const float v = Base::row_value(b, lane);                            // every lane holds the sum
             if (lane < peers.world) dst[static_cast<int64_t>(b) * peers.m_total + peers.row_base + m] = f32_to_bf16_rn(v);
-            Base::acc[b] = make_float2(0.f, 0.f);
         }
+        Base::clear();
     }
     // Results staged in shared memory leave for every rank at the end, consecutive threads writing
     // consecutive rows (coalesced peer stores instead of one 2-byte store per row and rank).
