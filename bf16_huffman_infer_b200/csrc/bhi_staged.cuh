@@ -1,6 +1,6 @@
 // Staged decode-side kernels for sm_100a.
 //
-// One persistent CTA per SM, 32 warps (16 for batches above 2, which need more registers).
+// One persistent CTA per SM, 32 warps (16 for batches above 4, which need more registers).
 //
 // Memory plan.  The exponent record of a (chunk, row) pair is contiguous in global memory; lane 0
 // of the warp that owns the row brings it into the warp's private shared-memory ring with ONE
@@ -916,7 +916,7 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
 template <class Codec, int B>
 static int staged_gemv_b(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
                          uint16_t *Y, cudaStream_t st) {
-    constexpr int NW = B <= 2 ? 32 : 16;
+    constexpr int NW = B <= 4 ? 32 : 16;      // measured: batches 5..8 are faster with 16 warps of twice the registers
     const int64_t K = static_cast<int64_t>(L.S) * L.Nc;
     const int64_t x_need = ((static_cast<int64_t>(B) * K * 2 + 255) / 256) * 256;
     if (x_need <= (NW == 16 ? kXStageMax16 : kXStageMax)) {
@@ -957,7 +957,7 @@ static int staged_gemv(const Layer &L, const typename Codec::Args &targs, const 
 template <class Codec, int B>
 static int staged_exchange_b(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X,
                              const PeerSet &peers, cudaStream_t st) {
-    constexpr int NW = B <= 2 ? 32 : 16;
+    constexpr int NW = B <= 4 ? 32 : 16;      // measured: batches 5..8 are faster with 16 warps of twice the registers
     const int64_t K = static_cast<int64_t>(L.S) * L.Nc;
     const int64_t x_need = ((static_cast<int64_t>(B) * K * 2 + 255) / 256) * 256;
     auto fill = [&](auto &sink) {
