@@ -87,3 +87,18 @@ def test_fused_siblings_give_the_same_tokens():
     graphed = get_graphed_model(model, cache)
     out = graphed.generate(ids.to(DEV), max_new_tokens=10, min_new_tokens=10, do_sample=False).cpu()
     assert torch.equal(out, eager)
+
+
+def test_decode_bench_example_runs():
+    """The whole-model example on a cut-down architecture: runs, reports both arms and a smaller model."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "bf16_huffman_infer_b200.examples.decode_bench", "--arch", "qwen3-1.7b",
+                          "--layers", "2", "--tokens", "8", "--prompt", "4"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["dense_bf16_tokens_per_s"] > 0 and line["compressed_tokens_per_s"] > 0
+    assert line["model_bytes_compressed"] < line["model_bytes_bf16"]
