@@ -512,11 +512,12 @@ class FusedCompressedLinear(nn.Module):
         self.weight = weight
         self.bias = bias
         self.splits = list(splits)            # [(start, stop), ...] in stacking order
+        self.sharded: Optional[nn.Module] = None   # set by tensor_parallel.shard_model_linears: computes the full output
         self._last_in = None
         self._last_out = None
 
     def run(self, input: Tensor) -> Tensor:
-        out = F.linear(input, self.weight, self.bias)
+        out = self.sharded(input) if self.sharded is not None else F.linear(input, self.weight, self.bias)
         self._last_in = (input.data_ptr(), input._version, tuple(input.shape))
         self._last_out = out
         return out

@@ -21,7 +21,7 @@ import torch.distributed as dist
 from torch import Tensor, nn
 
 from . import ops
-from .functional import FUSED_MAX_ROWS, ANSWeight, CompressedLinear, HuffmanWeight
+from .functional import FUSED_MAX_ROWS, ANSWeight, CompressedLinear, FusedCompressedLinear, HuffmanWeight
 
 __all__ = ["row_range", "shard_rows", "RowShardedLinear", "shard_model_linears", "PeerArena", "PeerRowShardedLinear"]
 
@@ -132,6 +132,9 @@ class PeerArena:
         self.base_ptrs: List[int] = []
         self.launches: Optional[Tensor] = None
 
+    def __deepcopy__(self, memo):
+        return self           # shared, peer-mapped state: copies of a model (e.g. its graphed twin) use the same arena
+
     def add(self, out_features: int) -> int:
         assert self.buffer is None, "the arena is already committed"
         nbytes = self.HEADER + ((FUSED_MAX_ROWS * out_features * 2 + 255) // 256) * 256
@@ -232,3 +235,12 @@ def shard_model_linears(model: nn.Module, rank: int, world: int, group=None, are
                 model.set_submodule(name, PeerRowShardedLinear.from_full(mod, arena, group))
             else:
                 model.set_submodule(name, RowShardedLinear.from_full(mod, rank, world, group))
+        elif isinstance(mod, FusedCompressedLinear) and mod.sharded is None and mod.weight.shape[0] % world == 0:
+            # stacked siblings: shard the stacked rows; the slices the siblings return stay views of the full output
+            full = CompressedLinear(mod.weight, mod.bias)
+            if arena is not None:
+                mod.sharded = PeerRowShardedLinear.from_full(full, arena, group)
+            else:
+                mod.sharded = RowShardedLinear.from_full(full, rank, world, group)
+            mod.weight = mod.sharded.local.weight          # keep only this rank's rows
+            mod.bias = None
