@@ -25,10 +25,17 @@
 // state' = freq * (state >> 8) + rem as one 32x32+64 multiply-add (a valid stream keeps
 // state < 2^40), refill word fetched from the ring.
 //
+// Multiply-accumulate (GEMV sinks).  One mma.sync.m16n8k16 per block and pair of batch rows, with the
+// words a lane has just rebuilt as its B fragment and its own X pairs as its A fragment; see the
+// comment above GemvSink.
+//
 // A warp owns whole output rows (all K-chunks in order): no cross-warp reduction, fixed
 // summation order.  Rows are dealt to CTAs in equal contiguous ranges and to the warps of a CTA
-// through a shared counter.  Records too large for the ring, or whose offsets are not in storage
-// order, are decoded from global memory by the table-exact decoder.
+// through a shared counter.  (Layers with few rows per CTA and several K-chunks are split by
+// record instead, with the partial sums added in chunk order at the end; row-sharded layers can
+// write their results into every rank's buffer: ExchangeSink.)  Records too large for the ring,
+// or whose offsets are not in storage order, are decoded from global memory by the table-exact
+// decoder.
 //
 // Every wait on an mbarrier is bounded; on expiry the warp records a status code in a device
 // word (bhi_debug_status), skips the record and carries on: a lost copy cannot hang the GPU.
@@ -72,7 +79,8 @@ constexpr uint32_t kRemMask = 0x807F807Fu;     // sign + mantissa bits of a bf16
 // shifts/adds on the (half-rate, saturated) integer pipe; because the compiler cannot see these
 // values it has to keep the multiply-add form.
 struct Consts {
-    uint32_t one, eight, entry, shift16;     // entry = bytes between consecutive fast-table entries (4 * copies)
+    uint32_t one, eight, entry, shift16;     // entry = bytes between consecutive fast-table entries (4 * copies);
+                                             // shift16 = 65536 (a left shift by 16 as a multiply)
 };
 
 // A prepared-table blob (Huffman): one copy of the folded pair table, then the exact tables.
@@ -131,19 +139,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-
-// packed FP32 fused multiply-add (two lanes per instruction on sm_100)
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-    uint64_t ra, rb, rc, rd;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
-    float2 d;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
-    return d;
-}
-__device__ __forceinline__ float2 bf16x2_to_f32x2(uint32_t p) { return make_float2(bf16lo_to_f32(p), bf16hi_to_f32(p)); }
 
 // ---- sinks: what happens to the two bf16x2 words a lane produces per 128-column block --------------
 // gblk = index of the 128-column block inside the full row (chunk * blocks_per_chunk + block).
@@ -617,7 +612,7 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
               uint32_t ring_bytes, Consts k, uint32_t part_bytes_arg, int split_arg) {
     const uint32_t part_bytes = kPart ? part_bytes_arg : 0u;
     const bool split = kPart && split_arg != 0;
-    extern __shared__ __align__(256) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     using Tables = typename Codec::Tables;
     using Dec = typename StagedOf<Codec>::type;
 
