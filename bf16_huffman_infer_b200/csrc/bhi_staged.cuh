@@ -710,12 +710,9 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     if (cur.valid && cur.staged) issue(cur, 0);
 
     BHI_TRACE_POINT(1);
-    // tables and X: overlaps the first copy in flight
+    // Tables first: they belong to the layer, so this still overlaps the previous kernel in the stream
+    // (and the first record copy in flight).
     Sink sink = sink_proto;
-    // Everything above read weights only.  X (and Y) belong to the previous kernel in the stream.
-    pdl_wait();
-    sink.after_wait(lane);
-    sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
     if (prepared == nullptr) {
         load_tables(tab, targs, threadIdx.x, blockDim.x);
         __syncthreads();
@@ -735,6 +732,10 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         for (int i = 0; i < kPer; i++)
             *reinterpret_cast<uint4 *>(fast + pair_slot(threadIdx.x + i * NW * 32)) = make_uint4(mine[i], mine[i], mine[i], mine[i]);
     }
+    // Everything above read weights only.  X (and Y) belong to the previous kernel in the stream.
+    pdl_wait();
+    sink.after_wait(lane);
+    sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
     __syncthreads();
 
     BHI_TRACE_POINT(2);
