@@ -52,13 +52,19 @@ def test_static_counters_match_caller_owned_counters():
     x1, x2 = make_input(3, K, 1).to(DEV), make_input(3, K, 2).to(DEV)
     both(x1, 7)                                       # set-up happens here (address lookup, counters cleared)
     torch.cuda.synchronize()
-    free_before, _ = torch.cuda.mem_get_info()
     for x in (x1, x2):                                # two calls in a row on the same slot
         a, b = both(x, 7)
         assert torch.equal(a, b)
         assert not torch.equal(a, torch.zeros_like(a))
     a, b = both(x1, 1023)                             # the last slot works, independently of slot 7
     assert torch.equal(a, b)
+    # nothing is allocated: free device memory is the same around calls that involve no torch allocation
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for slot in (7, 7, 500):
+        abi.check(abi.lib.bhi_gemv_bf16_huffman_exchange_static(p(w["rem"]), p(w["exp"]), words, p(x2), p(y_new), p(w["offsets"]),
+                                                                p(blob), S, M, K // S, 3, slot, abi.stream()))
+    torch.cuda.synchronize()
     free_after, _ = torch.cuda.mem_get_info()
     assert free_after == free_before, "device memory was allocated"
     status = C.c_int(-1)
