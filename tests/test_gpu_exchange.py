@@ -134,6 +134,30 @@ def test_single_rank_arena_matches_plain_layer(algo):
         assert torch.equal(peer(big), lin(big))                      # more than 8 rows: the ordinary path
 
 
+def test_results_too_large_to_stage_take_the_direct_stores(abi):
+    """Many rows per CTA at batch 8: the staged-result buffer would not fit, each row is stored by the lanes
+    that hold it; same results as the plain GEMV."""
+    M, K, B = 80000, 128, 8
+    Wb, shards = _shard("ans", M, K, 1, 4, 1)
+    X = make_input(B, K, 6)
+    x = X.to(DEV)
+    y = torch.zeros(8, M, dtype=torch.bfloat16, device=DEV)
+    counters = torch.zeros(2, 32, dtype=torch.int32, device=DEV)
+    launches = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ex = Exchange(world=1, rank=0, row_base=0, M_total=M)
+    ex.y[0] = y.data_ptr()
+    ex.ready[0] = counters[0].data_ptr()
+    ex.done[0] = counters[1].data_ptr()
+    ex.launches = launches.data_ptr()
+    for _ in range(2):
+        _launch(abi, "ans", shards[0], x, ex)
+    torch.cuda.synchronize()
+    assert _status(abi) == 0
+    plain = abi.gemv("ans", shards[0], x)
+    assert torch.equal(plain, y[:B])
+    assert rel_err(y[:B].float().cpu().numpy(), oracle.matvec(Wb, bits_of(X))) <= TOL
+
+
 def test_wait_on_a_missing_peer_runs_out(abi):
     """A peer that never signals: both bounded waits expire, the kernel ends, the status word says so and
     the context stays usable."""
