@@ -8,6 +8,7 @@
 #include "bhi_encode.cuh"
 #include "bhi_generic.cuh"
 #include "bhi_staged.cuh"
+#include "bhi_quad.cuh"
 #include "bhi_gemm.cuh"
 
 namespace bhi {
@@ -15,7 +16,9 @@ namespace bhi {
 static thread_local std::string g_error;
 static std::atomic<int> g_path{0};
 static std::atomic<int> g_overlap{0};
+static std::atomic<int> g_quad_ppw{1};
 bool overlap_launches() { return g_overlap.load() != 0; }
+int quad_passes_per_warp() { return g_quad_ppw.load(); }
 
 void set_error(const std::string &msg) { g_error = msg; }
 int fail(int code, const std::string &msg) {
@@ -62,7 +65,12 @@ static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uin
     BHI_REQUIRE(X && Y, "null activation buffer");
     BHI_REQUIRE(B >= 1 && B <= BHI_MAX_BATCH, "batch must be in [1, 8]");
     BHI_REQUIRE(aligned(X, 4) && aligned(Y, 2), "activation buffers must be 4-byte (X) / 2-byte (Y) aligned");
-    if (g_path.load() == 0) {
+    const int path = g_path.load();
+    if (path == 0) {
+        int rc = quad_launch<Codec>(L, targs, prepared, X, Y, nullptr, B, st);
+        if (rc != kStagedDeclined) return rc;
+    }
+    if (path == 0 || path == 2) {
         int rc = staged_gemv<Codec>(L, targs, prepared, X, Y, B, st);
         if (rc != kStagedDeclined) return rc;
     }
@@ -87,7 +95,7 @@ static int run_decode(const Layer &L, const typename Codec::Args &targs, const u
                       cudaStream_t st) {
     BHI_REQUIRE(Y, "null output buffer");
     BHI_REQUIRE(aligned(Y, 4), "output must be 4-byte aligned");
-    if (g_path.load() == 0) {
+    if (g_path.load() != 1) {
         int rc = staged_decode<Codec>(L, targs, prepared, Y, st);
         if (rc != kStagedDeclined) return rc;
     }
@@ -133,7 +141,9 @@ static int run_exchange(const Layer &L, const typename Codec::Args &targs, const
     peers.rank = ex->rank;
     peers.row_base = ex->row_base;
     peers.m_total = ex->M_total;
-    int rc = staged_exchange<Codec>(L, targs, prepared, X, peers, B, st);
+    int rc = kStagedDeclined;
+    if (g_path.load() == 0) rc = quad_launch<Codec>(L, targs, prepared, X, nullptr, &peers, B, st);
+    if (rc == kStagedDeclined) rc = staged_exchange<Codec>(L, targs, prepared, X, peers, B, st);
     return rc == kStagedDeclined ? fail(BHI_ERR_ARG, "shape not supported by the exchange kernel") : rc;
 }
 
@@ -188,6 +198,10 @@ const char *bhi_last_error(void) { return g_error.c_str(); }
 int bhi_abi_version(void) { return 1; }
 int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
 int bhi_set_launch_overlap(int on) { return g_overlap.exchange(on ? 1 : 0); }
+int bhi_set_quad_warps(int warps) {
+    if (warps != 16 && warps != 32) return -1;
+    return g_quad_ppw.exchange(warps == 16 ? 2 : 1) == 2 ? 16 : 32;
+}
 
 int bhi_debug_status(int *status_out) {
     BHI_REQUIRE(status_out, "null output");

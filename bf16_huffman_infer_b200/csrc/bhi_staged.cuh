@@ -70,9 +70,9 @@ constexpr int kGroup = 8;                      // blocks per rem prefetch group 
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // pair-table entry fields
-constexpr uint32_t kEntBits = 0xFu;            // bits 0..3: stream bits consumed
-constexpr uint32_t kEntSingle = 0x10u;         // only the first symbol is resolved
-constexpr uint32_t kEntExact = 0x20u;          // nothing resolved: use the exact tables
+constexpr uint32_t kEntBits = 0xFu;            // bits 0..3: stream bits consumed (bit 4 stays zero: the word is also a shift count)
+constexpr uint32_t kEntSingle = 0x20u;         // only the first symbol is resolved
+constexpr uint32_t kEntExact = 0x40u;          // nothing resolved: use the exact tables
 constexpr uint32_t kRemMask = 0x807F807Fu;     // sign + mantissa bits of a bf16x2 word; the rest is exponent
 
 // Multipliers handed to the kernel at launch.  Integer multiply-add runs on the FMA pipe, plain
@@ -444,7 +444,7 @@ __device__ __forceinline__ uint32_t resolve_symbol(const HuffTables &t, uint32_t
     return (n >= 9 && n <= known) ? n : 0;
 }
 
-// entry: bits 0..3 stream bits consumed, bit 4 single, bit 5 exact, bits 7..14 first exponent,
+// entry: bits 0..3 stream bits consumed, bit 5 single, bit 6 exact, bits 7..14 first exponent,
 // bits 16..19 length of the first symbol, bits 23..30 second exponent
 __device__ __forceinline__ uint32_t pair_entry(const HuffTables &t, uint32_t v) {
     uint32_t s0, s1;
@@ -859,15 +859,27 @@ static int staged_prepare(K kernel) {
 static bool staged_shape_ok(const Layer &L) { return aligned(L.rem, 16) && aligned(L.exp, 16); }
 
 
+// blob = folded pair table (one copy), exact tables, then one word: how many folded entries do not
+// resolve two symbols (0 lets the fused kernel run its loop without the per-step test)
 __global__ void __launch_bounds__(1024) huffman_prepare_kernel(HuffArgs targs, uint8_t *blob) {
     __shared__ HuffTables tab;
+    __shared__ uint32_t flagged;
+    if (threadIdx.x == 0) flagged = 0u;
     load_tables(tab, targs, threadIdx.x, blockDim.x);
     __syncthreads();
-    for (int v = threadIdx.x; v < kPairEntries; v += blockDim.x) reinterpret_cast<uint32_t *>(blob)[v] = pair_entry(tab, v);
+    uint32_t mine = 0;
+    for (int v = threadIdx.x; v < kPairEntries; v += blockDim.x) {
+        const uint32_t e = pair_entry(tab, v);
+        reinterpret_cast<uint32_t *>(blob)[v] = e;
+        mine += (e & (kEntSingle | kEntExact)) ? 1u : 0u;
+    }
+    if (mine) atomicAdd(&flagged, mine);
+    __syncthreads();
     uint32_t *dst = reinterpret_cast<uint32_t *>(blob + kPairEntries * 4);
     const uint32_t *src = reinterpret_cast<const uint32_t *>(&tab);
+    constexpr int kTabWords = static_cast<int>(sizeof(HuffTables) / 4);
     for (int i = threadIdx.x; i < kExactBytes / 4; i += blockDim.x)
-        dst[i] = i < static_cast<int>(sizeof(HuffTables) / 4) ? src[i] : 0u;
+        dst[i] = i < kTabWords ? src[i] : (i == kTabWords ? flagged : 0u);
 }
 
 template <class Codec, class Sink, int NW>

@@ -44,7 +44,7 @@ HUFFMAN_TABLES = os.environ.get("BHI_HUFFMAN_TABLES", "reference")
 def set_huffman_tables(method: str) -> str:
     """Choose the table builder used by later ``HuffmanWeight.compress`` calls; returns the previous choice."""
     global HUFFMAN_TABLES
-    assert method in ("reference", "escape"), method
+    assert method in ("reference", "escape") or (method.startswith("limit") and method[5:].isdigit()), method
     previous, HUFFMAN_TABLES = HUFFMAN_TABLES, method
     return previous
 

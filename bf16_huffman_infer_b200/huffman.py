@@ -38,7 +38,7 @@ except Exception:  # pragma: no cover
 SENTINEL = 255
 MAX_CODE_BITS = 32
 
-__all__ = ["LUTHuffmanEncoder", "SENTINEL", "MAX_CODE_BITS"]
+__all__ = ["LUTHuffmanEncoder", "SENTINEL", "MAX_CODE_BITS", "escape_byte_code", "length_limited_code"]
 
 
 class _HeapItem:
@@ -235,6 +235,23 @@ def escape_byte_code(freqs: Dict[int, float]) -> Dict[int, Tuple[int, int]]:
     return codes
 
 
+def length_limited_code(freqs: Dict[int, float], limit: int) -> Dict[int, Tuple[int, int]]:
+    """``{symbol: (length, value)}`` of the optimal prefix code whose lengths do not exceed ``limit`` (<= 8).
+
+    Every code fits the first byte table, so the byte-decomposed format holds it as it is.  With
+    ``limit = 6`` any two consecutive codes fit a 12-bit window: the fused kernels then resolve two
+    symbols with every table lookup and never take their symbol-by-symbol path.  Falls back to the
+    escape-byte code when there are more symbols than ``2**limit``.  No counterpart in the reference.
+    """
+    assert 1 <= limit <= 8
+    syms = sorted(freqs)
+    if len(syms) > (1 << limit):
+        return escape_byte_code(freqs)
+    lengths = _limited_lengths([freqs[s] for s in syms], limit)
+    paths = _canonical_paths(dict(zip(syms, lengths)))
+    return {s: (len(path), int(path[::-1], 2)) for s, path in paths.items()}
+
+
 class LUTHuffmanEncoder:
     """Drop-in for the reference class of the same name (``huffman.py:23-397``).
 
@@ -258,12 +275,16 @@ class LUTHuffmanEncoder:
     def build_lut(self, frequencies: Union[np.ndarray, Sequence[int], "torch.Tensor"], method: str = "reference") -> None:
         """``method='reference'`` reproduces the reference's code exactly; ``'escape'`` builds the
         escape-byte code (same table format, shorter frequent codes when the reference's repair loop
-        would have distorted them; no counterpart in the reference)."""
+        would have distorted them); ``'limitN'`` (N = 1..8) the optimal code with lengths <= N.  Neither of
+        the last two has a counterpart in the reference."""
         if torch is not None and torch.is_tensor(frequencies):
             frequencies = frequencies.cpu().numpy()
         freqs = {i: float(frequencies[i]) for i in range(256) if frequencies[i] > 0}
         if method == "escape":
             self._install(escape_byte_code(freqs))
+            return
+        if method.startswith("limit"):
+            self._install(length_limited_code(freqs, int(method[5:])))
             return
         assert method == "reference", method
         final = _repair_collisions(freqs, self.max_code_length)

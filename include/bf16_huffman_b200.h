@@ -44,10 +44,17 @@ const char *bhi_last_error(void);
 int bhi_abi_version(void);
 
 /* Which implementation the gemv / decode entry points use:
- *   0 = automatic (staged fast path when the shape allows it, else the generic path)
+ *   0 = automatic (the four-rows-per-warp-group kernel when the shape allows it, else the
+ *       one-row-per-warp staged kernel, else the generic path)
  *   1 = generic path only (one warp per record, direct global loads)
+ *   2 = skip the four-rows-per-warp-group kernel (one-row-per-warp staged kernel, else generic)
  * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
 int bhi_set_kernel_path(int path);
+
+/* Warps per block of the four-rows-per-warp-group kernel: 32 (a lane decodes two streams) or 16 (a lane
+ * decodes four streams, twice the registers per thread).  Process-wide; returns the previous value, -1 for
+ * a value other than 16 or 32.  For A/B measurements. */
+int bhi_set_quad_warps(int warps);
 
 /* Launch overlap (programmatic dependent launch), process-wide, off by default.  When on, a fused
  * kernel may begin while the previous kernel in the stream is still running: it reads the layer's

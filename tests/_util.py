@@ -98,6 +98,9 @@ class Abi:
     def set_path(self, path):
         return self.lib.bhi_set_kernel_path(C.c_int(path))
 
+    def set_quad_warps(self, warps):
+        return self.lib.bhi_set_quad_warps(C.c_int(warps))
+
     def prepare(self, w):
         """Fold the Huffman tables of `w` into a prepared blob (cached in the dict)."""
         if "_prepared" not in w:

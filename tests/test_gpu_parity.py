@@ -43,19 +43,38 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("path", [0, 1, 2], ids=["auto", "generic", "prepared"])
+# kernel variants of the fused product: (kernel path, warps of the four-row kernel, prepared tables)
+VARIANTS = {"auto": (0, 32, False), "generic": (1, 32, False), "prepared": (0, 32, True), "rowwarp": (2, 32, False),
+            "rowwarp-prepared": (2, 32, True), "quad16": (0, 16, False), "quad16-prepared": (0, 16, True)}
+PATHS = [(0, 32), (0, 16), (2, 32), (1, 32)]
+
+
+class use_path:
+    """Selects a kernel path (and the warp count of the four-row kernel) for the duration of a block."""
+
+    def __init__(self, abi, path, warps=32):
+        self.abi, self.path, self.warps = abi, path, warps
+
+    def __enter__(self):
+        self.prev = self.abi.set_path(self.path)
+        self.prev_warps = self.abi.set_quad_warps(self.warps)
+
+    def __exit__(self, *exc):
+        self.abi.set_path(self.prev)
+        self.abi.set_quad_warps(self.prev_warps)
+
+
+@pytest.mark.parametrize("variant", list(VARIANTS))
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
 @pytest.mark.parametrize("M,K,S,seed", SHAPES)
-def test_decode_and_gemv_match_oracle(abi, path, algo, M, K, S, seed):
-    prepared = path == 2
+def test_decode_and_gemv_match_oracle(abi, variant, algo, M, K, S, seed):
+    path, warps, prepared = VARIANTS[variant]
     if prepared and algo == "ans":
         pytest.skip("prepared tables exist for the Huffman coder only")
-    path = 0 if prepared else path
     W, Wb, tabs, rem, exp, offsets, _ = _layer(algo, M, K, S, seed)
     w = to_device(dict(rem=rem, exp=exp, offsets=offsets, **{k: v for k, v in tabs.items()
                                                           if k not in ("code_values", "freq", "cum")}), DEV)
-    prev = abi.set_path(path)
-    try:
+    with use_path(abi, path, warps):
         dense = abi.decode(algo, w, prepared=prepared)
         torch.cuda.synchronize()
         assert (bits_of(dense.cpu()) == Wb).all(), "decoded weight is not bit-exact"
@@ -67,8 +86,6 @@ def test_decode_and_gemv_match_oracle(abi, path, algo, M, K, S, seed):
         status = __import__("ctypes").c_int(-1)
         abi.check(abi.lib.bhi_debug_status(__import__("ctypes").byref(status)))
         assert status.value == 0, "a bounded wait expired inside a staged kernel"
-    finally:
-        abi.set_path(prev)
 
 
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
@@ -93,25 +110,28 @@ def test_pathological_tables_long_codes(abi):
     assert int(tabs["code_lengths"].max()) > 16
     rem, exp, offsets, _ = oracle.compress(Wb, "huffman", tabs, split_k=1)
     w = to_device(dict(rem=rem, exp=exp, offsets=offsets, **{k: tabs[k] for k in ("LUT1", "LUT2", "LUT3", "LUT4", "code_lengths")}), DEV)
-    for path in (0, 1):
-        prev = abi.set_path(path)
-        try:
+    X = make_input(2, 1024, 9)
+    ref = oracle.matvec(Wb, bits_of(X))
+    for path, warps in PATHS:
+        with use_path(abi, path, warps):
             assert (bits_of(abi.decode("huffman", w).cpu()) == Wb).all()
             assert (bits_of(abi.decode("huffman", w, prepared=True).cpu()) == Wb).all()
-            X = make_input(2, 1024, 9)
-            y = abi.gemv("huffman", w, X.to(DEV), prepared=True).float().cpu().numpy()
-            assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL
-        finally:
-            abi.set_path(prev)
+            for prepared in (True, False):
+                y = abi.gemv("huffman", w, X.to(DEV), prepared=prepared).float().cpu().numpy()
+                assert rel_err(y, ref) <= TOL, (path, warps, prepared)
 
 
+@pytest.mark.parametrize("method", ["escape", "limit6", "limit8"])
 @pytest.mark.parametrize("M,K,S,seed", [(384, 1024, 2, 4), (512, 4096, 1, 0), (128, 12288, 3, 0)])
-def test_escape_byte_tables_on_every_path(abi, M, K, S, seed):
-    """Tables from the alternative (escape-byte) builder: device encoder bytes equal the oracle's, all
-    decode paths are bit-exact, GEMV and the tensor-core product stay within tolerance."""
+def test_own_table_builders_on_every_path(abi, method, M, K, S, seed):
+    """Tables from the builders the reference does not have (escape-byte code, length-limited codes): device
+    encoder bytes equal the oracle's, all decode paths are bit-exact, GEMV and the tensor-core product stay
+    within tolerance.  With limit6 no 12-bit window is left unresolved, which selects the fused kernel's
+    loop without the per-step test."""
     W = make_weight(M, K, seed)
     Wb = bits_of(W)
-    tabs = tables_for("huffman", oracle.histogram(Wb), method="escape")
+    tabs = tables_for("huffman", oracle.histogram(Wb), method=method)
+    assert int(tabs["code_lengths"].max()) <= {"escape": 16, "limit6": 6, "limit8": 8}[method]
     rem, exp, offsets, L = oracle.compress(Wb, "huffman", tabs, split_k=S)
     g_rem, g_exp, g_off, g_rows = abi.encode("huffman", W.to(DEV), S, tabs)
     assert (g_rows.cpu().numpy() == L).all() and (g_off.cpu().numpy() == offsets).all()
@@ -119,16 +139,13 @@ def test_escape_byte_tables_on_every_path(abi, M, K, S, seed):
     w = to_device(dict(rem=rem, exp=exp, offsets=offsets, **{k: tabs[k] for k in ("LUT1", "LUT2", "LUT3", "LUT4", "code_lengths")}), DEV)
     X = make_input(8, K, seed)
     ref = oracle.matvec(Wb, bits_of(X))
-    for path in (0, 1):
-        prev = abi.set_path(path)
-        try:
+    for path, warps in PATHS:
+        with use_path(abi, path, warps):
             assert (bits_of(abi.decode("huffman", w).cpu()) == Wb).all()
             assert (bits_of(abi.decode("huffman", w, prepared=True).cpu()) == Wb).all()
-            for B in (1, 8):
+            for B in (1, 5, 8):
                 y = abi.gemv("huffman", w, X[:B].to(DEV), prepared=True).float().cpu().numpy()
-                assert rel_err(y, ref[:B]) <= TOL
-        finally:
-            abi.set_path(prev)
+                assert rel_err(y, ref[:B]) <= TOL, (path, warps, B)
     X = make_input(24, K, seed + 1)
     y = abi.linear("huffman", w, X.to(DEV), prepared=True).float().cpu().numpy()
     assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL
@@ -159,17 +176,14 @@ def test_reference_buffers_decode_and_multiply(abi, name):
     keys = ("LUT1", "LUT2", "LUT3", "LUT4", "code_lengths") if algo == "huffman" else ("LUT",)
     w = to_device({k: z[k] for k in ("rem", "exp", "offsets") + keys}, DEV)
     Wb = z["w_bits"]
-    for path in (0, 1):
-        prev = abi.set_path(path)
-        try:
+    for path, warps in PATHS:
+        with use_path(abi, path, warps):
             assert (bits_of(abi.decode(algo, w).cpu()) == Wb).all()
             X = torch.from_numpy(z["x_bits"].view(np.int16)).view(torch.bfloat16)
             for b in (1, 3, 8):
                 y = abi.gemv(algo, w, X[:b].to(DEV)).float().cpu().numpy()
                 assert rel_err(y, oracle.matvec(Wb, z["x_bits"][:b])) <= TOL
                 assert rel_err(y, z[f"ref_y_b{b}"]) <= TOL      # the reference's own fused output
-        finally:
-            abi.set_path(prev)
     tabs = tables_for(algo, oracle.histogram(Wb))
     W = torch.from_numpy(Wb.view(np.int16)).view(torch.bfloat16)
     g_rem, g_exp, g_off, _ = abi.encode(algo, W.to(DEV), z["rem"].shape[0], tabs)
