@@ -6,12 +6,19 @@ code_lengths}`` or ``.LUT``), but nothing rebuilds a :class:`CompressedLinear` f
 This module adds that step: ``save_compressed`` writes the state dict plus a small manifest of which
 modules are compressed (and how), ``load_compressed`` swaps the matching ``nn.Linear`` modules of a
 freshly constructed model for compressed ones and loads the buffers.
+
+On disk: one ``safetensors`` file - the format's tensors under their state-dict names, the manifest as a
+JSON string in the file's metadata.  Nothing is unpickled on load, and the manifest is checked against
+the model it is applied to (module names, layer shapes) before any module is replaced.
 """
 from __future__ import annotations
 
+import json
 from typing import Dict
 
 import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
 from torch import nn
 
 from .functional import (ANSWeight, CompressedLinear, FusedCompressedLinear, HuffmanWeight, _FusedSlice)
@@ -43,9 +50,48 @@ def compressed_manifest(model: nn.Module) -> Dict:
 
 
 def save_compressed(model: nn.Module, path: str) -> None:
-    """Write ``{"manifest": ..., "state_dict": ...}`` (CPU tensors) with ``torch.save``."""
-    state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
-    torch.save({"manifest": compressed_manifest(model), "state_dict": state}, path)
+    """Write the state dict (CPU tensors) as a safetensors file with the manifest in its metadata."""
+    state = {}
+    seen = {}
+    for k, v in model.state_dict().items():
+        t = v.detach().cpu().contiguous()
+        # safetensors refuses tensors that share storage (tied embeddings): store such a tensor once more
+        state[k] = t.clone() if t.data_ptr() in seen else t
+        seen[t.data_ptr()] = k
+    save_file(state, path, metadata={"manifest": json.dumps(compressed_manifest(model))})
+
+
+def _validate(model: nn.Module, manifest: Dict) -> None:
+    """The manifest must describe THIS model: every named module exists and is a linear layer of the shape the
+    compressed buffers encode (``rem`` is ``[S, out_features, in_features / S]``)."""
+    def check_shape(name: str, meta: Dict, out_features: int, in_features: int) -> None:
+        rem = meta.get("rem")
+        if (meta.get("algo") not in ("huffman", "ans") or not isinstance(rem, list) or len(rem) != 3
+                or rem[1] != out_features or rem[0] * rem[2] != in_features
+                or meta.get("offsets") != [rem[0], rem[1]] or not isinstance(meta.get("exp"), int) or meta["exp"] < 64):
+            raise ValueError(f"checkpoint entry {name!r} does not fit a linear layer {in_features} -> {out_features}: {meta}")
+
+    names = dict(model.named_modules())
+    for name, meta in manifest.get("modules", {}).items():
+        if meta.get("kind") == "linear":
+            old = names.get(name)
+            if not isinstance(old, nn.Linear):
+                raise ValueError(f"checkpoint names {name!r}, which is not an nn.Linear of this model")
+            check_shape(name, meta, old.out_features, old.in_features)
+        elif meta.get("kind") == "fused":
+            members = sorted((info["index"], n) for n, info in manifest.get("slices", {}).items() if info.get("owner") == name)
+            splits = meta.get("splits")
+            if not members or not isinstance(splits, list) or [i for i, _ in members] != list(range(len(splits))):
+                raise ValueError(f"stacked entry {name!r} has no consistent set of slices")
+            olds = [names.get(n) for _, n in members]
+            if not all(isinstance(o, nn.Linear) for o in olds):
+                raise ValueError(f"a slice of {name!r} is not an nn.Linear of this model")
+            if [list(sp) for sp in splits] != [[sum(o.out_features for o in olds[:i]), sum(o.out_features for o in olds[:i + 1])]
+                                               for i in range(len(olds))] or len({o.in_features for o in olds}) != 1:
+                raise ValueError(f"stacked entry {name!r} does not match the layers it replaces")
+            check_shape(name, meta, splits[-1][1], olds[0].in_features)
+        else:
+            raise ValueError(f"unknown entry kind in checkpoint: {meta.get('kind')!r}")
 
 
 def _empty_weight(meta: Dict) -> HuffmanWeight:
@@ -61,11 +107,15 @@ def _empty_weight(meta: Dict) -> HuffmanWeight:
 def load_compressed(model: nn.Module, path: str, strict: bool = True) -> nn.Module:
     """Turn ``model`` (same architecture, uncompressed, any initialisation) into the saved compressed
     model: the modules named in the manifest are replaced, then the state dict is loaded."""
-    blob = torch.load(path, map_location="cpu", weights_only=False)
-    manifest = blob["manifest"]
-    if manifest.get("format") != _FORMAT:
-        raise ValueError(f"not a compressed checkpoint of this package: {manifest.get('format')!r}")
-    state = blob["state_dict"]
+    with safe_open(path, framework="pt", device="cpu") as f:
+        meta = f.metadata() or {}
+        if "manifest" not in meta:
+            raise ValueError("not a compressed checkpoint of this package: no manifest in the file's metadata")
+        manifest = json.loads(meta["manifest"])
+        if not isinstance(manifest, dict) or manifest.get("format") != _FORMAT:
+            raise ValueError(f"not a compressed checkpoint of this package: {manifest.get('format') if isinstance(manifest, dict) else manifest!r}")
+        state = {k: f.get_tensor(k) for k in f.keys()}
+    _validate(model, manifest)
     owners = {}
     for name, meta in manifest["modules"].items():
         weight = _empty_weight(meta)

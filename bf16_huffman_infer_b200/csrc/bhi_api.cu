@@ -3,6 +3,7 @@
 // device on first use), so every call can be captured into a CUDA graph.
 #include <atomic>
 #include <mutex>
+#include <unordered_map>
 
 #include "bhi_common.cuh"
 #include "bhi_encode.cuh"
@@ -16,9 +17,20 @@ namespace bhi {
 static thread_local std::string g_error;
 static std::atomic<int> g_path{0};
 static std::atomic<int> g_overlap{0};
-static std::atomic<int> g_quad_ppw{1};
+static std::atomic<int> g_quad_ppw{0};
 bool overlap_launches() { return g_overlap.load() != 0; }
 int quad_passes_per_warp() { return g_quad_ppw.load(); }
+
+// Prepared blobs the caller has declared pair-complete (bhi_huffman_table_hint): device pointer -> true.
+// A tuning hint only; bhi_huffman_prepare forgets the entry of the blob it rewrites.
+static std::mutex g_hint_mu;
+static std::unordered_map<const void *, bool> g_hints;
+static bool pair_complete_hint(const void *prepared) {
+    if (prepared == nullptr) return false;
+    std::lock_guard<std::mutex> lock(g_hint_mu);
+    auto it = g_hints.find(prepared);
+    return it != g_hints.end() && it->second;
+}
 
 void set_error(const std::string &msg) { g_error = msg; }
 int fail(int code, const std::string &msg) {
@@ -66,8 +78,17 @@ static int run_gemv(const Layer &L, const typename Codec::Args &targs, const uin
     BHI_REQUIRE(B >= 1 && B <= BHI_MAX_BATCH, "batch must be in [1, 8]");
     BHI_REQUIRE(aligned(X, 4) && aligned(Y, 2), "activation buffers must be 4-byte (X) / 2-byte (Y) aligned");
     const int path = g_path.load();
+    const bool complete = pair_complete_hint(prepared);
+    // One or two rows of X with rANS, or with Huffman tables that have unresolved windows: the one-row-per-warp
+    // kernel is the faster one there (its single-symbol detour is cheaper, and its tensor-core tile covers two
+    // rows of X anyway)
+    const bool row_first = !(std::is_same<Codec, HuffCodec>::value && complete) && B <= 2;
+    if (path == 0 && row_first) {
+        int rc = staged_gemv<Codec>(L, targs, prepared, X, Y, B, st);
+        if (rc != kStagedDeclined) return rc;
+    }
     if (path == 0) {
-        int rc = quad_launch<Codec>(L, targs, prepared, X, Y, nullptr, B, st);
+        int rc = quad_launch<Codec>(L, targs, prepared, X, Y, nullptr, B, complete, st);
         if (rc != kStagedDeclined) return rc;
     }
     if (path == 0 || path == 2) {
@@ -142,14 +163,19 @@ static int run_exchange(const Layer &L, const typename Codec::Args &targs, const
     peers.row_base = ex->row_base;
     peers.m_total = ex->M_total;
     int rc = kStagedDeclined;
-    if (g_path.load() == 0) rc = quad_launch<Codec>(L, targs, prepared, X, nullptr, &peers, B, st);
+    const bool complete = pair_complete_hint(prepared);
+    const bool row_first = !(std::is_same<Codec, HuffCodec>::value && complete) && B <= 2;
+    if (g_path.load() == 0 && !row_first) rc = quad_launch<Codec>(L, targs, prepared, X, nullptr, &peers, B, complete, st);
     if (rc == kStagedDeclined) rc = staged_exchange<Codec>(L, targs, prepared, X, peers, B, st);
+    if (rc == kStagedDeclined && g_path.load() == 0 && row_first) rc = quad_launch<Codec>(L, targs, prepared, X, nullptr, &peers, B, complete, st);
     return rc == kStagedDeclined ? fail(BHI_ERR_ARG, "shape not supported by the exchange kernel") : rc;
 }
 
 // ---- exchange counters kept inside the library (bhi_gemv_bf16_huffman_exchange_static) --------------
 // One 256-byte entry per layer slot: ready counter at word 0, done counter at word 32, launch counter at
-// word 48.  File-scope device memory: nothing is allocated; the address is looked up once per device.
+// word 48, block-arrival counter at word 49.  File-scope device memory: nothing is allocated; the address is
+// looked up once per device.  No clearing: a file-scope device array without initialiser is zero when the
+// module is loaded, and a clear enqueued on the first caller's stream could run under another stream's kernel.
 constexpr int kStaticWordsPerLayer = 64;
 static __device__ __align__(256) uint32_t g_static_exchange[BHI_STATIC_EXCHANGE_LAYERS * kStaticWordsPerLayer];
 
@@ -167,8 +193,6 @@ static int static_exchange_base(cudaStream_t st, uint32_t **base_out) {
         void *p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_exchange);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress");
-        e = cudaMemsetAsync(p, 0, sizeof(uint32_t) * BHI_STATIC_EXCHANGE_LAYERS * kStaticWordsPerLayer, st);   // counters start at zero
-        if (e != cudaSuccess) return cuda_fail(e, "clearing the exchange counters");
         base[dev] = static_cast<uint32_t *>(p);
     }
     *base_out = base[dev];
@@ -199,8 +223,16 @@ int bhi_abi_version(void) { return 1; }
 int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
 int bhi_set_launch_overlap(int on) { return g_overlap.exchange(on ? 1 : 0); }
 int bhi_set_quad_warps(int warps) {
-    if (warps != 16 && warps != 32) return -1;
-    return g_quad_ppw.exchange(warps == 16 ? 2 : 1) == 2 ? 16 : 32;
+    if (warps != 0 && warps != 16 && warps != 32) return -1;
+    const int prev = g_quad_ppw.exchange(warps == 16 ? 2 : warps == 32 ? 1 : 0);
+    return prev == 2 ? 16 : prev == 1 ? 32 : 0;
+}
+int bhi_huffman_table_hint(const uint8_t *prepared, int pair_complete) {
+    BHI_REQUIRE(prepared, "null prepared tables");
+    std::lock_guard<std::mutex> lock(g_hint_mu);
+    if (pair_complete) g_hints[prepared] = true;
+    else g_hints.erase(prepared);
+    return BHI_OK;
 }
 
 int bhi_debug_status(int *status_out) {
@@ -254,6 +286,10 @@ int bhi_huffman_prepare(const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t 
     BHI_REQUIRE(LUT1 && LUT2 && LUT3 && LUT4 && code_lengths && prepared, "null table");
     BHI_REQUIRE(aligned(prepared, 16), "prepared tables must be 16-byte aligned");
     HuffArgs t{LUT1, LUT2, LUT3, LUT4, code_lengths};
+    {
+        std::lock_guard<std::mutex> lock(g_hint_mu);
+        g_hints.erase(prepared);
+    }
     huffman_prepare_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(t, prepared);
     return launch_status("huffman_prepare launch");
 }

@@ -56,15 +56,24 @@ struct QuadGeom {
 
 __device__ __forceinline__ uint32_t lds32(const uint8_t *smem, uint32_t a) { return *reinterpret_cast<const uint32_t *>(smem + a); }
 
+// barrier among the warps of one group: hardware barrier group + 1 (0 is the CTA-wide one).  Literal
+// barrier numbers, so that the kernel reserves nine barriers and not all sixteen.
 __device__ __forceinline__ void group_barrier(int group, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(threads) : "memory");
+#define BHI_GROUP_BAR(g) \
+    case g: asm volatile("bar.sync " #g " + 1, %0;" ::"r"(threads) : "memory"); break;
+    switch (group) {
+        BHI_GROUP_BAR(0) BHI_GROUP_BAR(1) BHI_GROUP_BAR(2) BHI_GROUP_BAR(3)
+        BHI_GROUP_BAR(4) BHI_GROUP_BAR(5) BHI_GROUP_BAR(6) BHI_GROUP_BAR(7)
+    }
+#undef BHI_GROUP_BAR
 }
 
 // ---- Huffman, symbol by symbol (rare windows) --------------------------------------------------------
 // Decodes the next four symbols of one stream with first-symbol lookups (and the exact cascade for
 // codes longer than the table index).  `p` is the true bit cursor.  Returns the two entry words
-// {block A, block B} with the exponents at bits 7..14 and 23..30.
-__device__ __noinline__ uint2 quad_huff_slow(uint32_t p, uint32_t off, uint32_t plim, uint32_t copy_shift, uint32_t lut_bytes,
+// {block A, block B} with the exponents at bits 7..14 and 23..30.  Inlined: as a call it cost a
+// quarter more on tables where a few percent of the windows need it.
+__device__ __forceinline__ uint2 quad_huff_slow(uint32_t p, uint32_t off, uint32_t plim, uint32_t copy_shift, uint32_t lut_bytes,
                                              uint32_t *p_out) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const HuffTables &t = *reinterpret_cast<const HuffTables *>(smem + lut_bytes);
@@ -420,17 +429,19 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
             bool next_first = false;
 
             auto mac = [&](int pp, int blk, uint32_t rw, uint32_t e0, uint32_t e1) {
-                const uint4 a = xq[blk * (16 * B) + pp * (B * 4)];
+                uint4 a = make_uint4(0u, 0u, 0u, 0u);
+                if (B == 8 || gq < B) a = xq[blk * (16 * B) + pp * (B * 4)];     // lanes of unused batch rows feed zeros
                 mma_bf16_16x8x16(c[pp], a.x, a.y, a.z, a.w, bitselect(prmt(rw, 0u, 0x1100u), e0, kRemMask),
                                  bitselect(prmt(rw, 0u, 0x3322u), e1, kRemMask));
             };
 
             if (cur.staged) {
-                if (!have_first) {
+                const int full = nblk / kRG;                // groups of kRG blocks whose sign/mantissa words are prefetched
+                if (full > 0 && !have_first) {
 #pragma unroll
                     for (int pp = 0; pp < PPW; pp++)
 #pragma unroll
-                        for (int j = 0; j < kRG; j++) r_cur[pp][j] = (j < nblk) ? __ldg(rem + j * 32 + pp * 8) : 0u;
+                        for (int j = 0; j < kRG; j++) r_cur[pp][j] = __ldg(rem + j * 32 + pp * 8);
                 }
                 const bool arrived = mbar_wait_bounded(bar0 + 8u * slot, (phases >> slot) & 1u);
                 phases ^= 1u << slot;
@@ -440,39 +451,23 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                     for (int pp = 0; pp < PPW; pp++) dec[pp].open(ctx, cur.base + r * cur.stride(), sigma4 + 32u * pp, cur.rows);
                     auto run = [&](auto checked_tag) {
                         constexpr bool kChecked = decltype(checked_tag)::value;
-                        for (int g0 = 0; g0 < nblk; g0 += kRG) {
-                            const bool last = g0 + kRG >= nblk;
+                        for (int gi = 0; gi < full; gi++) {
+                            // next group of this record, or the first group of the next unit (of this one again if there is none)
+                            const uint32_t *src = (gi + 1 < full) ? rem + (gi + 1) * (kRG * 32) : rem_next;
 #pragma unroll
                             for (int pp = 0; pp < PPW; pp++)
 #pragma unroll
-                                for (int j = 0; j < kRG; j++) {
-                                    if (!last) r_nxt[pp][j] = (g0 + kRG + j < nblk) ? __ldg(rem + (g0 + kRG + j) * 32 + pp * 8) : 0u;
-                                    else r_nxt[pp][j] = (nxt.valid && j < nblk) ? __ldg(rem_next + j * 32 + pp * 8) : 0u;
-                                }
-                            if (g0 + kRG <= nblk) {
+                                for (int j = 0; j < kRG; j++) r_nxt[pp][j] = __ldg(src + j * 32 + pp * 8);
+                            const int g0 = gi * kRG;
 #pragma unroll
-                                for (int j = 0; j < kRG; j += 2) {
-                                    uint32_t eA0[PPW], eA1[PPW], eB0[PPW], eB1[PPW];
+                            for (int j = 0; j < kRG; j += 2) {
+                                uint32_t eA0[PPW], eA1[PPW], eB0[PPW], eB1[PPW];
 #pragma unroll
-                                    for (int pp = 0; pp < PPW; pp++) dec[pp].template two<kChecked>(ctx, eA0[pp], eA1[pp], eB0[pp], eB1[pp]);
+                                for (int pp = 0; pp < PPW; pp++) dec[pp].template two<kChecked>(ctx, eA0[pp], eA1[pp], eB0[pp], eB1[pp]);
 #pragma unroll
-                                    for (int pp = 0; pp < PPW; pp++) {
-                                        mac(pp, g0 + j, r_cur[pp][j], eA0[pp], eA1[pp]);
-                                        mac(pp, g0 + j + 1, r_cur[pp][j + 1], eB0[pp], eB1[pp]);
-                                    }
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < kRG; j += 2) {
-                                    if (g0 + j < nblk) {
-#pragma unroll
-                                        for (int pp = 0; pp < PPW; pp++) {
-                                            uint32_t eA0, eA1, eB0, eB1;
-                                            dec[pp].template two<kChecked>(ctx, eA0, eA1, eB0, eB1);
-                                            mac(pp, g0 + j, r_cur[pp][j], eA0, eA1);
-                                            if (g0 + j + 1 < nblk) mac(pp, g0 + j + 1, r_cur[pp][j + 1], eB0, eB1);
-                                        }
-                                    }
+                                for (int pp = 0; pp < PPW; pp++) {
+                                    mac(pp, g0 + j, r_cur[pp][j], eA0[pp], eA1[pp]);
+                                    mac(pp, g0 + j + 1, r_cur[pp][j + 1], eB0[pp], eB1[pp]);
                                 }
                             }
 #pragma unroll
@@ -482,10 +477,20 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                                 for (int j = 0; j < kRG; j++) r_cur[pp][j] = r_nxt[pp][j];
                             }
                         }
+                        // blocks past the last full group: sign/mantissa words fetched on the spot
+                        for (int blk = full * kRG; blk < nblk; blk += 2) {
+#pragma unroll
+                            for (int pp = 0; pp < PPW; pp++) {
+                                uint32_t eA0, eA1, eB0, eB1;
+                                dec[pp].template two<kChecked>(ctx, eA0, eA1, eB0, eB1);
+                                mac(pp, blk, __ldg(rem + blk * 32 + pp * 8), eA0, eA1);
+                                if (blk + 1 < nblk) mac(pp, blk + 1, __ldg(rem + (blk + 1) * 32 + pp * 8), eB0, eB1);
+                            }
+                        }
                     };
                     if (checked) run(std::true_type{});
                     else run(std::false_type{});
-                    next_first = nxt.valid;
+                    next_first = nxt.valid && full > 0;
                 } else if (lane == 0) {
                     atomicExch(&g_staged_status, 1);
                 }
@@ -559,15 +564,7 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
             for (int q = 0; q < kMaxPeers; q++)
                 if (q < peers.world) peers.y[q][at] = v;
         }
-        // The barrier orders every warp's stores before the signalling lanes; their release at system
-        // scope is cumulative over it (the pattern of a grid-wide barrier: bar.sync, then one fence + atomic).
-        __syncthreads();
-        if (tid < peers.world) red_release_sys_add(pick(peers.done, tid), 1u);
-        if (blockIdx.x == 0 && tid == 0) {
-            if (!counter_wait_bounded(pick(peers.done, peers.rank), launch_no * peers.world * gridDim.x)) atomicExch(&g_staged_status, 9);
-            *peers.launches = launch_no;
-            __threadfence();
-        }
+        exchange_finish(peers, launch_no);
     }
 }
 
@@ -620,7 +617,7 @@ static bool quad_plan(const Layer &L, int grid, bool exchange, QuadGeom &G, uint
     return false;
 }
 
-int quad_passes_per_warp();      // process-wide choice between the 32-warp and the 16-warp form, see bhi_set_quad_warps
+int quad_passes_per_warp();      // 0 = by table kind, 1 = 32 warps, 2 = 16 warps: see bhi_set_quad_warps
 
 template <class Codec, int B, int PPW>
 static int quad_launch_p(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X, uint16_t *Y,
@@ -650,27 +647,34 @@ static int quad_launch_p(const Layer &L, const typename Codec::Args &targs, cons
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "quad kernel launch");
 }
 
+// pair_complete: the caller knows that every window of the folded table resolves two symbols (no code
+// longer than kPairBits / 2).  Such tables run fastest with two warps per group (a lane decodes four
+// streams); tables with unresolved windows with four warps per group, where the divergent
+// symbol-by-symbol detour stalls half as many streams.  Only a tuning hint: the kernel itself reads
+// from the table header whether it may skip the per-step test.
 template <class Codec, int B>
 static int quad_launch_b(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X, uint16_t *Y,
-                         const PeerSet *peers, cudaStream_t st) {
-    if (quad_passes_per_warp() == 2) return quad_launch_p<Codec, B, 2>(L, targs, prepared, X, Y, peers, st);
+                         const PeerSet *peers, bool pair_complete, cudaStream_t st) {
+    int ppw = quad_passes_per_warp();
+    if (ppw == 0) ppw = (pair_complete || !std::is_same<Codec, HuffCodec>::value) ? 2 : 1;
+    if (ppw == 2) return quad_launch_p<Codec, B, 2>(L, targs, prepared, X, Y, peers, st);
     return quad_launch_p<Codec, B, 1>(L, targs, prepared, X, Y, peers, st);
 }
 
 template <class Codec>
 static int quad_launch(const Layer &L, const typename Codec::Args &targs, const uint8_t *prepared, const uint16_t *X, uint16_t *Y,
-                       const PeerSet *peers, int B, cudaStream_t st) {
+                       const PeerSet *peers, int B, bool pair_complete, cudaStream_t st) {
     if (!staged_shape_ok(L) || !aligned(prepared, 16)) return kStagedDeclined;
     if (static_cast<int64_t>(L.S) * L.M >= (1ll << 31)) return kStagedDeclined;
     switch (B) {
-        case 1: return quad_launch_b<Codec, 1>(L, targs, prepared, X, Y, peers, st);
-        case 2: return quad_launch_b<Codec, 2>(L, targs, prepared, X, Y, peers, st);
-        case 3: return quad_launch_b<Codec, 3>(L, targs, prepared, X, Y, peers, st);
-        case 4: return quad_launch_b<Codec, 4>(L, targs, prepared, X, Y, peers, st);
-        case 5: return quad_launch_b<Codec, 5>(L, targs, prepared, X, Y, peers, st);
-        case 6: return quad_launch_b<Codec, 6>(L, targs, prepared, X, Y, peers, st);
-        case 7: return quad_launch_b<Codec, 7>(L, targs, prepared, X, Y, peers, st);
-        case 8: return quad_launch_b<Codec, 8>(L, targs, prepared, X, Y, peers, st);
+        case 1: return quad_launch_b<Codec, 1>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 2: return quad_launch_b<Codec, 2>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 3: return quad_launch_b<Codec, 3>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 4: return quad_launch_b<Codec, 4>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 5: return quad_launch_b<Codec, 5>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 6: return quad_launch_b<Codec, 6>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 7: return quad_launch_b<Codec, 7>(L, targs, prepared, X, Y, peers, pair_complete, st);
+        case 8: return quad_launch_b<Codec, 8>(L, targs, prepared, X, Y, peers, pair_complete, st);
     }
     return kStagedDeclined;
 }

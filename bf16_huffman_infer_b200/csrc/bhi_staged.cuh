@@ -298,14 +298,18 @@ struct DenseSink {
 // Every rank computes the rows [row_base, row_base + M) of Y [B, M_total] and needs all of it.  Instead
 // of a collective after the kernel, the lanes that hold a finished dot product store it straight into
 // the Y buffer of every rank (plain stores to peer-mapped pointers over NVLink; lane r serves rank r).
-// Three counter words per layer and rank make that safe without any other kernel:
+// Four counter words per layer and rank make that safe without any other kernel:
 //   ready  - each rank adds 1 on every peer when its launch may be written to (its earlier consumers of
 //            Y are done: the add comes after the wait for the previous kernel in the stream); a warp
 //            checks its own copy (>= world * launch number) before its first remote store;
-//   done   - each CTA adds 1 on every peer after its stores (release at system scope); the kernel does
-//            not end before the local copy shows world * grid * launch number, so whatever runs next
-//            on the stream sees the whole of Y;
+//   arrive (local) - every CTA adds 1 after its stores; the CTA that brings it to grid * launch number is
+//            the last one of this launch on this GPU;
+//   done   - that last CTA adds 1 on every peer (release at system scope, cumulative over all CTAs'
+//            stores through the arrive counter) and then waits until its own copy shows
+//            world * launch number, so whatever runs next on the stream sees the whole of Y.  One
+//            system-scope signal per peer and launch, whatever the grids of the ranks are;
 //   launches (local) - how often this layer has run; written by the one waiting thread at the end.
+// launches and arrive are two consecutive words (PeerSet::launches points at the first).
 // Both waits are bounded; on expiry the status word is set (8 = peers not ready, 9 = peers not done)
 // and the kernel carries on.
 constexpr int kMaxPeers = BHI_MAX_PEERS;
@@ -363,6 +367,30 @@ __device__ __forceinline__ T pick(T const (&a)[kMaxPeers], int i) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t *p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
+// End of an exchange kernel (every thread of the CTA calls it after its stores to the peers).
+__device__ __forceinline__ void exchange_finish(const PeerSet &peers, uint32_t launch_no) {
+    // The barrier orders every warp's stores before thread 0; its release is cumulative over them, and the
+    // last CTA's acquire of the arrive counter, then its release at system scope, carry them to the peers.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t before = atom_add_acq_rel_gpu(peers.launches + 1, 1u);
+        if (before + 1u == launch_no * gridDim.x) {
+#pragma unroll
+            for (int q = 0; q < kMaxPeers; q++)
+                if (q < peers.world) red_release_sys_add(peers.done[q], 1u);
+            if (!counter_wait_bounded(pick(peers.done, peers.rank), launch_no * peers.world)) atomicExch(&g_staged_status, 9);
+            *peers.launches = launch_no;
+            __threadfence();
+        }
+    }
+}
+
 template <int B, bool kXS>
 struct ExchangeSink : GemvSink<B, kXS> {
     using Base = GemvSink<B, kXS>;
@@ -403,17 +431,7 @@ struct ExchangeSink : GemvSink<B, kXS> {
                 if (q < peers.world) peers.y[q][at] = v;
         }
     }
-    __device__ __forceinline__ void finish_kernel() {
-        // The barrier orders every warp's stores before the signalling lanes; their release at system
-        // scope is cumulative over it (the pattern of a grid-wide barrier: bar.sync, then one fence + atomic).
-        __syncthreads();
-        if (threadIdx.x < peers.world) red_release_sys_add(pick(peers.done, threadIdx.x), 1u);
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            if (!counter_wait_bounded(pick(peers.done, peers.rank), launch_no * peers.world * gridDim.x)) atomicExch(&g_staged_status, 9);
-            *peers.launches = launch_no;
-            __threadfence();
-        }
-    }
+    __device__ __forceinline__ void finish_kernel() { exchange_finish(peers, launch_no); }
 };
 
 // ---- Huffman: folded pair table ---------------------------------------------------------------------

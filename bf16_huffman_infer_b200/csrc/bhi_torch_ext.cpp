@@ -132,6 +132,13 @@ void boxed_huffman_prepare(StableIValue *stack, uint64_t, uint64_t) {
     check(bhi_huffman_prepare(t[0], t[1], t[2], t[3], t[4], ptr<uint8_t>(blob), stream_of(blob)));
 }
 
+// huffman_table_hint(prepared, pair_complete) -> ()
+void boxed_huffman_table_hint(StableIValue *stack, uint64_t, uint64_t) {
+    Tensor blob = arg(stack, 0);
+    want(blob, ScalarType::Byte, "prepared");
+    check(bhi_huffman_table_hint(ptr<const uint8_t>(blob), static_cast<int>(iarg(stack, 1))));
+}
+
 // gemv_bf16_huffman_prepared(A_rem, A_exp, X, Y(a!), offsets, prepared) -> ()
 void boxed_gemv_bf16_huffman_prepared(StableIValue *stack, uint64_t, uint64_t) {
     Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
@@ -461,6 +468,7 @@ STABLE_TORCH_LIBRARY(BHI_TORCH_NAMESPACE, m) {
     m.def("ans_decode(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor LUT) -> ()");
     // prepared Huffman tables
     m.def("huffman_prepare(Tensor LUT1, Tensor LUT2, Tensor LUT3, Tensor LUT4, Tensor code_lengths, Tensor(a!) prepared) -> ()");
+    m.def("huffman_table_hint(Tensor prepared, int pair_complete) -> ()");
     m.def("gemv_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("huffman_decode_prepared(Tensor A_rem, Tensor A_exp, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
     m.def("linear_bf16_huffman_prepared(Tensor A_rem, Tensor A_exp, Tensor X, Tensor(a!) Y, Tensor offsets, Tensor prepared) -> ()");
@@ -487,6 +495,7 @@ STABLE_TORCH_LIBRARY_IMPL(BHI_TORCH_NAMESPACE, CUDA, m) {
     m.impl("ans_encode", &boxed_ans_encode);
     m.impl("ans_decode", &boxed_ans_decode);
     m.impl("huffman_prepare", &boxed_huffman_prepare);
+    m.impl("huffman_table_hint", &boxed_huffman_table_hint);
     m.impl("gemv_bf16_huffman_prepared", &boxed_gemv_bf16_huffman_prepared);
     m.impl("huffman_decode_prepared", &boxed_huffman_decode_prepared);
     m.impl("linear_bf16_huffman_prepared", &boxed_linear_bf16_huffman_prepared);

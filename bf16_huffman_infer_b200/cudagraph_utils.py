@@ -13,9 +13,17 @@ the model derives positions and masks from it, so the captured step takes the to
 works for any batch size the cache was built for.  Graphs are captured lazily, one per batch size,
 the first time a one-token step of that size is seen (i.e. after the prompt has been processed,
 when the cache tensors exist).
+
+``generate`` hands every step an attention mask and position ids.  Without padding both carry no
+information beyond the cache's fill level (the mask is all ones, every sequence sits at the same
+position), so the captured step - which lets the model derive them from the cache - is used
+whenever the mask of the call is all ones; the check is made once per ``generate`` call on the
+mask the caller passed.  A batch with padding runs eagerly (with a one-time warning).  How often
+each path ran is kept in ``model.graph_stats``.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, Optional
 
 import torch
@@ -72,23 +80,51 @@ def _room_for_capture(cache) -> bool:
     return True
 
 
+def _all_ones(mask) -> Optional[bool]:
+    """True / False for a 2-D mask tensor (costs a synchronisation), None for forms that are not inspected."""
+    if mask is None:
+        return True
+    if torch.is_tensor(mask) and mask.dim() == 2:
+        return bool(mask.all())
+    return None
+
+
 def apply_graphed(model: nn.Module, cache, replace_generate: bool = True) -> None:
     """Swap ``model.forward`` (and ``model.generate``) for the graph-replaying versions, in place."""
     old_forward = model.forward
     graphs: Dict[int, _StepGraph] = {}
+    stats = {"captures": 0, "replays": 0, "eager_steps": 0}
+    model.graph_stats = stats
+    # None outside generate(); inside: whether the mask the caller passed was free of padding
+    state = {"no_padding": None, "warned": False}
+
+    def trivial_inputs(attention_mask, position_ids) -> bool:
+        if state["no_padding"] is not None:
+            return state["no_padding"]
+        if attention_mask is None and position_ids is None:
+            return True
+        # a direct call with a mask: inspect it (a synchronisation); position ids cannot be checked cheaply
+        return position_ids is None and _all_ones(attention_mask) is True
 
     def forward(input_ids: Optional[torch.LongTensor] = None, attention_mask=None, position_ids=None,
                 past_key_values=None, inputs_embeds=None, **kwargs) -> CausalLMOutputWithPast:
         one_token = (input_ids is not None and input_ids.dim() == 2 and input_ids.shape[1] == 1 and input_ids.is_cuda
-                     and attention_mask is None and position_ids is None and inputs_embeds is None
-                     and not torch.is_grad_enabled())
-        if one_token:
+                     and inputs_embeds is None and not torch.is_grad_enabled())
+        if one_token and trivial_inputs(attention_mask, position_ids):
             batch = input_ids.shape[0]
             step = graphs.get(batch)
             if step is None and _room_for_capture(cache):
                 step = graphs[batch] = _StepGraph(old_forward, cache, batch, input_ids.device)
+                stats["captures"] += 1
             if step is not None:
+                stats["replays"] += 1
                 return CausalLMOutputWithPast(logits=step(input_ids), past_key_values=cache)
+        if one_token:
+            stats["eager_steps"] += 1
+            if not state["warned"]:
+                state["warned"] = True
+                warnings.warn("one-token step run eagerly: the batch has padding (or explicit position ids), "
+                              "which the captured CUDA graph does not take as inputs")
         kwargs.pop("use_cache", None)
         kwargs.pop("return_dict", None)
         return old_forward(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
@@ -102,8 +138,19 @@ def apply_graphed(model: nn.Module, cache, replace_generate: bool = True) -> Non
         def generate(*args, **kwargs):
             cache.reset()
             kwargs.pop("past_key_values", None)
-            with torch.no_grad():
-                return old_generate(*args, past_key_values=cache, disable_compile=True, **kwargs)
+            verdict = _all_ones(kwargs.get("attention_mask"))
+            if kwargs.get("attention_mask") is None:
+                # generate() derives a mask from pad tokens in the prompt when it is given none
+                ids = kwargs.get("input_ids", args[0] if args else None)
+                pad = getattr(getattr(model, "generation_config", None), "pad_token_id", None)
+                if torch.is_tensor(ids) and pad is not None and bool((ids == pad).any()):
+                    verdict = False
+            state["no_padding"] = bool(verdict)          # uninspectable forms count as padded
+            try:
+                with torch.no_grad():
+                    return old_generate(*args, past_key_values=cache, disable_compile=True, **kwargs)
+            finally:
+                state["no_padding"] = None
 
         model.generate = generate
 

@@ -35,10 +35,16 @@ FUSED_MAX_ROWS = 8        # up to here: fused decode + GEMV; beyond: decode, the
 # instead of decode + GEMM.  Off by default: on B200 it is correct but slower than decode + library GEMM
 # (its tensor-core instructions are issued for 32 weight rows at a time).  BHI_TENSOR_ROWS=128 turns it on.
 TENSOR_MAX_ROWS = int(os.environ.get("BHI_TENSOR_ROWS", "0"))
-# Which prefix code HuffmanWeight.compress builds: "reference" reproduces the reference's tables (and so its
-# compressed bytes) exactly; "escape" uses the escape-byte builder of huffman.py (same table format, readable
-# by any decoder of the format, near-entropy on every histogram).  See set_huffman_tables().
-HUFFMAN_TABLES = os.environ.get("BHI_HUFFMAN_TABLES", "reference")
+# Which prefix code HuffmanWeight.compress builds (huffman.py; every choice yields tables of the reference's
+# format, readable by any decoder of it, the reference's included):
+#   "limit6"    (default) optimal code with no length above 6 bits: any two codes fit the 12-bit index of the fused
+#               kernels' folded table, so they never leave their two-symbols-per-lookup loop (fastest; about 4 %
+#               larger than "escape" on N(0, s) weights; falls back to "escape" beyond 64 distinct exponents);
+#   "escape"    escape-byte code, near-entropy on every histogram (smallest);
+#   "reference" the reference's own builder, bit for bit (and so its compressed bytes); on some histograms its
+#               repair loop lengthens the frequent codes by 2 bits.
+# See set_huffman_tables() and convert_all_linear(huffman_tables=...).
+HUFFMAN_TABLES = os.environ.get("BHI_HUFFMAN_TABLES", "limit6")
 
 
 def set_huffman_tables(method: str) -> str:
@@ -231,11 +237,15 @@ class HuffmanWeight(nn.Module):
         first call has to happen outside CUDA-graph capture; warm-up iterations take care of that).
         Not a buffer: it is derived data and stays out of ``state_dict`` and size accounting."""
         blob = self.__dict__.get("_prepared")
-        if blob is None or blob.device != self.rem.device or self.__dict__.get("_prepared_src") != self.LUT1.data_ptr():
+        tables = (self.LUT1, self.LUT2, self.LUT3, self.LUT4, self.code_lengths)
+        src = tuple((t.data_ptr(), t._version) for t in tables)      # in-place loads (load_state_dict) bump the version
+        if blob is None or blob.device != self.rem.device or self.__dict__.get("_prepared_src") != src:
             blob = torch.empty(ops.PREPARED_BYTES, dtype=torch.uint8, device=self.rem.device)
-            ops.huffman_prepare(self.LUT1, self.LUT2, self.LUT3, self.LUT4, self.code_lengths, blob)
+            ops.huffman_prepare(*tables, blob)
+            # codes of at most 6 bits: every 12-bit window holds two whole codes (the kernels pick their warp layout by it)
+            ops.huffman_table_hint(blob, int(self.code_lengths.max().item()) <= 6)
             self.__dict__["_prepared"] = blob
-            self.__dict__["_prepared_src"] = self.LUT1.data_ptr()
+            self.__dict__["_prepared_src"] = src
         return blob
 
     def get_weight(self) -> Tensor:
@@ -515,18 +525,28 @@ class FusedCompressedLinear(nn.Module):
         self.sharded: Optional[nn.Module] = None   # set by tensor_parallel.shard_model_linears: computes the full output
         self._last_in = None
         self._last_out = None
+        self._readers_left = 0                      # slices that have not picked up the last output yet
 
     def run(self, input: Tensor) -> Tensor:
         out = self.sharded(input) if self.sharded is not None else F.linear(input, self.weight, self.bias)
         self._last_in = (input.data_ptr(), input._version, tuple(input.shape))
         self._last_out = out
+        self._readers_left = len(self.splits) - 1
         return out
 
     def cached(self, input: Tensor) -> Tensor:
+        """The leader's output for this very input.  It is kept only until every other slice has read it once:
+        a later tensor that happens to get the same address (and version 0) must not match a stale entry."""
         key = (input.data_ptr(), input._version, tuple(input.shape))
         if self._last_out is None or self._last_in != key:
-            return self.run(input)
-        return self._last_out
+            out = self.run(input)
+            self._readers_left -= 1
+        else:
+            out = self._last_out
+            self._readers_left -= 1
+        if self._readers_left <= 0:
+            self._last_in = self._last_out = None
+        return out
 
 
 class _FusedSlice(nn.Module):

@@ -70,6 +70,12 @@ def huffman_prepare(LUT1: Tensor, LUT2: Tensor, LUT3: Tensor, LUT4: Tensor, code
     _ops.huffman_prepare.default(LUT1, LUT2, LUT3, LUT4, code_lengths, prepared)
 
 
+def huffman_table_hint(prepared: Tensor, pair_complete: bool) -> None:
+    """Tell the library that no code of the table behind ``prepared`` is longer than 6 bits (a tuning hint for
+    the fused kernels' warp layout; results do not depend on it).  See ``bhi_huffman_table_hint``."""
+    _ops.huffman_table_hint.default(prepared, int(bool(pair_complete)))
+
+
 def gemv_bf16_huffman_prepared(A_rem: Tensor, A_exp: Tensor, X: Tensor, Y: Tensor, offsets: Tensor, prepared: Tensor) -> None:
     _ops.gemv_bf16_huffman_prepared.default(A_rem, A_exp, X, Y, offsets, prepared)
 

@@ -155,7 +155,7 @@ class PeerArena:
         else:
             self.buffer = torch.zeros(self._total, dtype=torch.uint8, device=self.device)
             self.base_ptrs = [self.buffer.data_ptr()]
-        self.launches = torch.zeros(len(self._sizes), dtype=torch.int32, device=self.device)
+        self.launches = torch.zeros(2 * len(self._sizes), dtype=torch.int32, device=self.device)   # per layer: launches, block arrivals
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(self.group)          # every rank's counters are zero before anybody launches
@@ -172,7 +172,7 @@ class PeerArena:
         y = [b + off + self.HEADER for b in self.base_ptrs]
         ready = [b + off for b in self.base_ptrs]
         done = [b + off + 128 for b in self.base_ptrs]
-        return torch.tensor(y + ready + done + [self.launches.data_ptr() + 4 * slot], dtype=torch.int64)
+        return torch.tensor(y + ready + done + [self.launches.data_ptr() + 8 * slot], dtype=torch.int64)
 
 
 class PeerRowShardedLinear(nn.Module):

@@ -92,4 +92,10 @@ def shallow_copy_model(model: nn.Module) -> nn.Module:
         memo[id(p)] = p
     for b in model.buffers():
         memo[id(b)] = b
+    # derived device data a module keeps outside its buffers (e.g. the folded decode tables of a compressed weight)
+    # is shared too: a copy would cost memory and lose what the native library remembers about the original
+    for m in model.modules():
+        for v in vars(m).values():
+            if torch.is_tensor(v):
+                memo[id(v)] = v
     return copy.deepcopy(model, memo=memo)

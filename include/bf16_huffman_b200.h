@@ -51,9 +51,10 @@ int bhi_abi_version(void);
  * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
 int bhi_set_kernel_path(int path);
 
-/* Warps per block of the four-rows-per-warp-group kernel: 32 (a lane decodes two streams) or 16 (a lane
- * decodes four streams, twice the registers per thread).  Process-wide; returns the previous value, -1 for
- * a value other than 16 or 32.  For A/B measurements. */
+/* Warps per block of the four-rows-per-warp-group kernel: 32 (a lane decodes two streams), 16 (a lane
+ * decodes four streams, twice the registers per thread) or 0 = chosen per call (16 for rANS and for Huffman
+ * tables declared pair-complete, see bhi_huffman_table_hint; else 32).  Process-wide; returns the previous
+ * value, -1 for any other argument.  For A/B measurements. */
 int bhi_set_quad_warps(int warps);
 
 /* Launch overlap (programmatic dependent launch), process-wide, off by default.  When on, a fused
@@ -97,6 +98,12 @@ int bhi_huffman_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_
  * fetch it with a single bulk copy.  Results are identical.  No counterpart in the reference
  * (its kernels index the byte tables directly, src/kernel.cu:370-377). */
 int bhi_huffman_prepared_bytes(void);
+/* Tuning hint for a prepared blob (host-side bookkeeping, no device work): pair_complete != 0 declares that
+ * no code of the table is longer than 6 bits, so that any two consecutive codes fit the 12-bit index of the
+ * folded table.  The fused kernels pick their warp layout by it; results never depend on it (whether the
+ * per-step test can be skipped is read from the blob itself).  bhi_huffman_prepare clears the hint of the
+ * blob it writes; give the hint after preparing.  Thread-safe. */
+int bhi_huffman_table_hint(const uint8_t *prepared, int pair_complete);
 int bhi_huffman_prepare(const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3, const uint8_t *LUT4,
                         const uint8_t *code_lengths, uint8_t *prepared, void *stream);
 int bhi_gemv_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
@@ -147,8 +154,10 @@ int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp
  * same order.  No counterpart in the reference (single GPU).
  *
  * ready[r], done[r]: one u32 word per rank for THIS layer, in peer-mapped memory, zero before the
- * first call and never touched by the caller afterwards; launches: one u32 word in local memory,
- * zero before the first call.  The kernel signals the peers that y may be overwritten only after
+ * first call and never touched by the caller afterwards; launches: TWO consecutive u32 words in local
+ * memory (the layer's launch counter, then the kernel's block-arrival counter), zero before the first
+ * call.  Every rank signals each peer once per launch, whatever its grid, so the ranks may hold
+ * different numbers of rows.  The kernel signals the peers that y may be overwritten only after
  * everything earlier in `stream` has finished, so consumers of Y must be ordered on the same
  * stream.  Waits on peers are bounded (one second each); if one runs out the status word is set
  * (bhi_debug_status) and Y is incomplete.  batch <= BHI_MAX_BATCH, world <= BHI_MAX_PEERS. */
@@ -168,13 +177,13 @@ int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int6
                                int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
 
 /* Single-GPU form of bhi_gemv_bf16_huffman_exchange whose counter words live inside the library
- * (no counterpart in the reference).  Y [batch, M] is an ordinary output buffer; the three counter
- * words of the exchange protocol (ready, done, launches) are taken from a file-scope device array of
+ * (no counterpart in the reference).  Y [batch, M] is an ordinary output buffer; the counter
+ * words of the exchange protocol (ready, done, launches, block arrivals) are taken from a file-scope device array of
  * BHI_STATIC_EXCHANGE_LAYERS entries of 256 bytes (256 KB per device), entry `layer_slot`; slots
  * outside [0, BHI_STATIC_EXCHANGE_LAYERS) are rejected with BHI_ERR_LIMIT.  Nothing is allocated:
- * the array's address is looked up once per device and the array is cleared then (the first call on
- * a device must therefore not be made while `stream` is being captured; it returns BHI_ERR_ARG if it
- * is).  Calls that use the same slot and may overlap in time (different streams, or threads) race on
+ * the array's address is looked up once per device (the first call on a device must therefore not be
+ * made while `stream` is being captured; it returns BHI_ERR_ARG if it is); the array needs no clearing,
+ * device memory of this kind starts out zero when the library is loaded.  Calls that use the same slot and may overlap in time (different streams, or threads) race on
  * its counters and must be serialised by the caller; different slots are independent. */
 #define BHI_STATIC_EXCHANGE_LAYERS 1024
 int bhi_gemv_bf16_huffman_exchange_static(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,

@@ -76,6 +76,30 @@ def rel_err(y, y_ref):
     return float(excess.max() / max(np.sqrt((y_ref ** 2).mean()), 1e-30))
 
 
+def raw_rel_err(y, y_ref):
+    """max |y - y_ref| / rms(y_ref) with nothing taken off: the figure the 1e-2 bound is quoted on, BF16 output
+    rounding included (it alone reaches 1e-2 rms for an output of 2.6 rms, see rel_err)."""
+    y = np.asarray(y, np.float64)
+    y_ref = np.asarray(y_ref, np.float64)
+    return float(np.abs(y - y_ref).max() / max(np.sqrt((y_ref ** 2).mean()), 1e-30))
+
+
+def bf16_round(v):
+    """Round-to-nearest-even of float values to BF16, returned as float64."""
+    t = torch.from_numpy(np.asarray(v, np.float64)).to(torch.float32).to(torch.bfloat16)
+    return t.to(torch.float64).numpy()
+
+
+def ulp_excess(y, y_ref):
+    """How far |y - bf16(y_ref)| exceeds one BF16 ulp of y_ref, in units of rms(y_ref); <= 0 means every output
+    is the correctly rounded value or its neighbour.  (An FP32 accumulation in another order than the
+    reference's moves a sum by a few 1e-7 relative, enough to cross a rounding boundary, never two.)"""
+    y = np.asarray(y, np.float64)
+    y_ref = np.asarray(y_ref, np.float64)
+    excess = np.abs(y - bf16_round(y_ref)) - 2.0 * bf16_half_ulp(y_ref)
+    return float(excess.max() / max(np.sqrt((y_ref ** 2).mean()), 1e-30))
+
+
 class Abi:
     """ctypes access to libbf16_huffman_b200.so taking torch CUDA tensors (data pointers only)."""
 
@@ -109,6 +133,7 @@ class Abi:
             p = self.p
             self.check(self.lib.bhi_huffman_prepare(p(w["LUT1"]), p(w["LUT2"]), p(w["LUT3"]), p(w["LUT4"]),
                                                     p(w["code_lengths"]), p(blob), self.stream()))
+            self.check(self.lib.bhi_huffman_table_hint(p(blob), int(int(w["code_lengths"].max().item()) <= 6)))
             w["_prepared"] = blob
         return w["_prepared"]
 

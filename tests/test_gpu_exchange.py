@@ -3,7 +3,7 @@
 Two ranks are played one after the other on the same device: each "rank" stores its slice of the
 output into both ranks' buffers.  Kernels that wait for one another must never be separate launches
 on one GPU, so the counters a launch would wait for are credited by the host beforehand (the peer's
-"ready" and its per-CTA "done" arrivals); no launch then waits for another.  The multi-process form
+"ready" and its "done" signal); no launch then waits for another.  The multi-process form
 over NVLink is covered by test_gpu_exchange_multi.py on boxes with two GPUs.
 """
 import ctypes as C
@@ -65,10 +65,6 @@ def _launch(abi, algo, w, x, ex):
     abi.check(rc)
 
 
-def _grid(rows):
-    return min(torch.cuda.get_device_properties(0).multi_processor_count, rows)
-
-
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
 @pytest.mark.parametrize("M,K,S,B", [(256, 1024, 2, 1), (512, 4096, 1, 3), (384, 512, 1, 8)])
 def test_two_ranks_played_in_turn(abi, algo, M, K, S, B):
@@ -79,8 +75,7 @@ def test_two_ranks_played_in_turn(abi, algo, M, K, S, B):
     ref = oracle.matvec(Wb, bits_of(X))
     y = [torch.zeros(8, M, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
     counters = torch.zeros(world, 2, 32, dtype=torch.int32, device=DEV)      # [rank, ready/done, padded]
-    launches = torch.zeros(world, dtype=torch.int32, device=DEV)
-    grid = _grid(M // world)
+    launches = torch.zeros(world, 2, dtype=torch.int32, device=DEV)      # per rank: launch counter, block-arrival counter
     for call in range(3):                                                    # the counters keep counting across calls
         for r in range(world):
             ex = Exchange(world=world, rank=r, row_base=M * r // world, M_total=M)
@@ -88,25 +83,25 @@ def test_two_ranks_played_in_turn(abi, algo, M, K, S, B):
                 ex.y[q] = y[q].data_ptr()
                 ex.ready[q] = counters[q, 0].data_ptr()
                 ex.done[q] = counters[q, 1].data_ptr()
-            ex.launches = launches[r:].data_ptr()
+            ex.launches = launches[r].data_ptr()
             # what the other rank would have signalled by now on rank r's words
             if r == 0:
                 counters[r, 0, 0] += 1
-                counters[r, 1, 0] += grid
+                counters[r, 1, 0] += 1
             _launch(abi, algo, shards[r], x, ex)
             torch.cuda.synchronize()
             if r == 0:
                 # rank 1 really signals below: take the credit back out of rank 0's words first, so that
-                # they end this call at exactly world * launch number (and world * grid * launch number)
+                # both end this call at exactly world * launch number
                 counters[r, 0, 0] -= 1
-                counters[r, 1, 0] -= grid
+                counters[r, 1, 0] -= 1
         assert _status(abi) == 0
         for q in range(world):
             got = y[q][:B].float().cpu().numpy()
             assert rel_err(got, ref) <= TOL, (call, q)
         assert counters[:, 0, 0].tolist() == [world * (call + 1)] * world
-        assert counters[:, 1, 0].tolist() == [world * grid * (call + 1)] * world
-        assert launches.tolist() == [call + 1] * world
+        assert counters[:, 1, 0].tolist() == [world * (call + 1)] * world
+        assert launches[:, 0].tolist() == [call + 1] * world
         for t in y:
             t.zero_()
 
@@ -143,7 +138,7 @@ def test_results_too_large_to_stage_take_the_direct_stores(abi):
     x = X.to(DEV)
     y = torch.zeros(8, M, dtype=torch.bfloat16, device=DEV)
     counters = torch.zeros(2, 32, dtype=torch.int32, device=DEV)
-    launches = torch.zeros(1, dtype=torch.int32, device=DEV)
+    launches = torch.zeros(2, dtype=torch.int32, device=DEV)
     ex = Exchange(world=1, rank=0, row_base=0, M_total=M)
     ex.y[0] = y.data_ptr()
     ex.ready[0] = counters[0].data_ptr()

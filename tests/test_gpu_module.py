@@ -19,16 +19,21 @@ TOL = 1e-2
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("algo", ["huffman", "ans"])
+@pytest.mark.parametrize("algo,method", [("huffman", "reference"), ("huffman", "limit6"), ("huffman", "escape"), ("ans", None)])
 @pytest.mark.parametrize("M,K", [(256, 512), (128, 12288), (384, 4096)])
-def test_compress_matches_oracle_and_decodes(algo, M, K):
-    from bf16_huffman_infer_b200 import ANSWeight, HuffmanWeight
+def test_compress_matches_oracle_and_decodes(algo, method, M, K):
+    from bf16_huffman_infer_b200 import ANSWeight, HuffmanWeight, set_huffman_tables
     W = make_weight(M, K, 11)
     cls = HuffmanWeight if algo == "huffman" else ANSWeight
-    cw = cls.compress(W)
+    previous = set_huffman_tables(method) if method else None
+    try:
+        cw = cls.compress(W)
+    finally:
+        if method:
+            set_huffman_tables(previous)
     assert cw.rem.device.type == "cpu"            # like the reference, compress hands back CPU tensors
     Wb = bits_of(W)
-    tabs = (huffman_tables if algo == "huffman" else ans_tables)(oracle.histogram(Wb))[0]
+    tabs = huffman_tables(oracle.histogram(Wb), method)[0] if algo == "huffman" else ans_tables(oracle.histogram(Wb))[0]
     rem, exp, offsets, _ = oracle.compress(Wb, algo, tabs)
     assert (cw.rem.numpy() == rem).all() and (cw.exp.numpy() == exp).all() and (cw.offsets.numpy() == offsets).all()
     if algo == "huffman":

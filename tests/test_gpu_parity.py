@@ -44,15 +44,16 @@ SHAPES = [
 
 
 # kernel variants of the fused product: (kernel path, warps of the four-row kernel, prepared tables)
-VARIANTS = {"auto": (0, 32, False), "generic": (1, 32, False), "prepared": (0, 32, True), "rowwarp": (2, 32, False),
-            "rowwarp-prepared": (2, 32, True), "quad16": (0, 16, False), "quad16-prepared": (0, 16, True)}
-PATHS = [(0, 32), (0, 16), (2, 32), (1, 32)]
+VARIANTS = {"auto": (0, 0, False), "auto-prepared": (0, 0, True), "generic": (1, 0, False),
+            "rowwarp": (2, 0, False), "rowwarp-prepared": (2, 0, True),
+            "quad32": (0, 32, False), "quad32-prepared": (0, 32, True), "quad16": (0, 16, False), "quad16-prepared": (0, 16, True)}
+PATHS = [(0, 0), (0, 32), (0, 16), (2, 0), (1, 0)]
 
 
 class use_path:
     """Selects a kernel path (and the warp count of the four-row kernel) for the duration of a block."""
 
-    def __init__(self, abi, path, warps=32):
+    def __init__(self, abi, path, warps=0):
         self.abi, self.path, self.warps = abi, path, warps
 
     def __enter__(self):

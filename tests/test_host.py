@@ -127,7 +127,7 @@ def test_compressed_checkpoint_roundtrip(tmp_path):
     src.q_proj = _FusedSlice(owner, 0, True)
     src.k_proj = _FusedSlice(owner, 1, False)
     src.o_proj = CompressedLinear(compressed("ans", 512, 512, 2), None)
-    path = str(tmp_path / "model.pt")
+    path = str(tmp_path / "model.safetensors")
     save_compressed(src, path)
 
     dst = load_compressed(Block().to(torch.bfloat16), path)
@@ -138,3 +138,15 @@ def test_compressed_checkpoint_roundtrip(tmp_path):
     assert a.keys() == b.keys()
     for k in a:
         assert torch.equal(a[k], b[k]), k
+    # a manifest that does not describe the model it is applied to is refused before anything is replaced
+    class Other(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = torch.nn.Linear(512, 256, bias=True)
+            self.k_proj = torch.nn.Linear(512, 128, bias=True)
+            self.o_proj = torch.nn.Linear(256, 512, bias=False)      # other input width
+            self.norm = torch.nn.LayerNorm(512)
+    other = Other().to(torch.bfloat16)
+    with pytest.raises(ValueError, match="does not fit"):
+        load_compressed(other, path)
+    assert isinstance(other.q_proj, torch.nn.Linear)
