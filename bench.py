@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload qwen3-8b+fused|qwen3-8b|llama3-70b[+fused]|tiny|layer:MxK|stack:NxMxK]
-                    [--algo huffman|ans|smallest] [--tables escape|reference] [--batch B] [--exchange peer|nccl]
+                    [--algo huffman|ans|smallest] [--tables limit6|escape|reference] [--batch B] [--exchange peer|nccl]
 
 One "step" is one decode token's worth of the hot path: every compressed linear layer of a
 decoder of the named shape applied once, in model order, to a batch of B activation rows (B = 1
@@ -19,9 +19,17 @@ Printed JSON line (rank 0):
            against the measured HBM copy bandwidth of MEASURED_PEAKS.json;
   cpu_baseline  the CPU restatement of the reference's fused path (oracle/, all host threads) on a
            bounded sample of the same workload;
-  reference_tables  (one GPU, Huffman) the same stack encoded with the reference's own table builder
-           instead of the escape-byte builder, timed the same way;
+  other_tables  (one GPU, Huffman) the same stack encoded with the other table builders ("escape": smallest;
+           "reference": the reference's own, byte-identical buffers), timed the same way;
+  ans      the same stack with the rANS coder;
+  batch_sweep  tokens/s of the same stack at batch 1, 2, 4, 8 with the uncompressed torch stack beside each;
+  per_shape  every Qwen3-8B linear shape x both coders on its own: time per launch over more than L2 of distinct
+           copies, compressed GB/s, fraction of the measured HBM peak;
+  reference_gpu  the reference's own kernels built for sm_100a on the same shapes (a subprocess);
+  llama3_70b  the Llama-3-70B-shape stack, timed the same way (rows sharded over the ranks when N > 1);
   dense_bf16_torch  the uncompressed stack as torch nn.Linear layers on the same GPU.
+With N > 1 one extra, untimed step compares every layer's exchanged output with an NCCL all-gather of the
+ranks' slices (`exchange_verified`).
 `--impl reference` times the CPU path alone and prints the same line shape.
 With N > 1 (launched under torchrun) every layer is sharded by output rows across the ranks; the
 slices are put together by the kernel's own epilogue (stores into every rank's buffer over NVLink,
@@ -50,8 +58,27 @@ WORKLOADS = {
     "llama3-70b": (80, 8192, 28672, 64, 8, 128, 128256),
     "tiny": (2, 1024, 3072, 8, 2, 128, 8192),
 }
-# ncu: dram bytes read+written per launch / algorithmic bytes, fused Huffman GEMV, 4096x4096, B=1
-TRAFFIC_OVER_ALGORITHMIC = 1.0014
+# DRAM bytes read + written per launch / algorithmic bytes of the fused Huffman GEMV, from the ncu capture
+# summarised in profiles/quad_gemv_huffman_12288x4096_b1.md (dram__bytes_read.sum + dram__bytes_write.sum)
+TRAFFIC_OVER_ALGORITHMIC = 1.004
+QWEN3_SHAPES = {"q_o": (4096, 4096), "k_v": (1024, 4096), "gate_up": (12288, 4096), "down": (4096, 12288)}
+
+
+def host_threads():
+    """Cores this process may use (launchers export OMP_NUM_THREADS=1, which must not shrink the CPU arm)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def load_by_path(name, rel):
+    """A pure-Python module of the package by file path: the CPU arm must not load the package's native libraries."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, rel))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def fuse_shapes(shapes):
@@ -144,8 +171,9 @@ def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference"):
     weight count."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle
-    from bf16_huffman_infer_b200.ans import RANSEncoder
-    from bf16_huffman_infer_b200.huffman import LUTHuffmanEncoder
+    RANSEncoder = load_by_path("_bench_ans_tables", "bf16_huffman_infer_b200/ans.py").RANSEncoder
+    LUTHuffmanEncoder = load_by_path("_bench_huffman_tables", "bf16_huffman_infer_b200/huffman.py").LUTHuffmanEncoder
+    oracle.set_threads(host_threads())
 
     def tables_for_bits(a, bits):
         hist = oracle.histogram(bits)
@@ -262,8 +290,84 @@ def run_step(mods, meta, xs, batch):
     return out
 
 
-def ours(args, rank, world, dev):
+def capture_step(mods, meta, xs, B):
+    """Warm up eagerly (this also folds the decode tables), then capture one pass over the stack as a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(2):
+            run_step(mods, meta, xs, B)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        y_static = run_step(mods, meta, xs, B)
+    return graph, y_static
+
+
+def timed_region(fn, steps, world, dev):
+    """CUDA-event time of `steps` calls of fn, bracketed by barrier + synchronize, max over ranks (ms)."""
     import torch.distributed as dist
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def quick_tokens_per_s(mods, meta, dev, B, steps, world=1):
+    """tokens/s of the stack at batch B (graph replay, activations resident): for the sweeps beside the headline."""
+    hidden = meta[0]["K"] if "K" in meta[0] else mods[0].in_features
+    xs = {"hidden": torch.randn(B, hidden, device=dev).to(torch.bfloat16)}
+    graph, _ = capture_step(mods, meta, xs, B)
+    for _ in range(3):
+        graph.replay()
+    ms = timed_region(graph.replay, steps, world, dev) / steps
+    del graph
+    return B / (ms * 1e-3), ms
+
+
+def verify_exchange(mods, meta, xs, B, world):
+    """One untimed pass: every layer's exchanged output against an NCCL all-gather of the ranks' own slices."""
+    import torch.distributed as dist
+    ok = True
+    with torch.no_grad():
+        h = xs["hidden"]
+        q = gate = None
+        for mod, info in zip(mods, meta):
+            kind = info["name"].split(".")[-1]
+            x = q if kind == "o_proj" else gate if kind == "down_proj" else h
+            full = mod(x).clone()
+            part = mod.local(x).contiguous()
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            ok = ok and torch.equal(full, torch.cat(parts, dim=-1))
+            if kind.startswith("q_proj"):
+                q = full[..., :info["q_rows"]] if "q_rows" in info else full
+            elif kind.startswith("gate_proj"):
+                gate = full[..., :info["first_rows"]] if "first_rows" in info else full
+    flag = torch.tensor([1.0 if ok else 0.0], device=xs["hidden"].device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item() == 1.0)
+
+
+def ours(args, rank, world, dev, light=False):
+    """Builds and times one stack.  light=True: device-resident timing only (for the side runs)."""
     from bf16_huffman_infer_b200 import set_huffman_tables
 
     t_setup = time.time()
@@ -277,39 +381,8 @@ def ours(args, rank, world, dev):
     torch.cuda.synchronize()
     setup_s = time.time() - t_setup
 
-    # warm up eagerly (also folds the decode tables), then capture the step as one CUDA graph
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side), torch.no_grad():
-        for _ in range(2):
-            run_step(mods, meta, xs, B)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph), torch.no_grad():
-        y_static = run_step(mods, meta, xs, B)
+    graph, y_static = capture_step(mods, meta, xs, B)
     y_host = torch.empty(y_static.shape, dtype=y_static.dtype).pin_memory()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
     def e2e_step():
         xs["hidden"].copy_(x_host, non_blocking=True)
@@ -317,15 +390,18 @@ def ours(args, rank, world, dev):
         y_host.copy_(y_static, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
+    steps = max(3, args.steps // 4) if light else args.steps
     for _ in range(max(args.warmup, 3)):
         graph.replay()
     with ClockSampler(dev.index) as clocks:
-        ms = timed(graph.replay, args.steps)
-    for _ in range(2):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
+        ms = timed_region(graph.replay, steps, world, dev)
+    ms_e2e = None
+    if not light:
+        for _ in range(2):
+            e2e_step()
+        ms_e2e = timed_region(e2e_step, steps, world, dev)
 
-    ms_step = ms / args.steps
+    ms_step = ms / steps
     launches_per_step = len(mods)
     alg_bytes = sum(m["bytes"] + B * m["K"] * 2 + B * m["local_rows"] * 2 for m in meta)
     peak, peak_kind = peaks()
@@ -333,7 +409,7 @@ def ours(args, rank, world, dev):
     total_bytes_all_ranks = alg_bytes * world
     line = {
         "metric": "decode tokens/s (hot path: all compressed linear layers of one token)", "value": B / (ms_step * 1e-3),
-        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights decoded from u8+entropy-coded u8, fp32 accumulate",
         "data": "synthetic", "impl": "ours",
         "config": {
@@ -348,23 +424,105 @@ def ours(args, rank, world, dev):
                          "results stored into every rank's buffer by the kernel's epilogue (peer memory over NVLink)"
                          if args.exchange == "peer" and not meta[0].get("exchange_fallback") else "NCCL all-gather after every matrix"),
         },
-        "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(x_host.numel() * 2),
-                "d2h_bytes_per_step": int(y_host.numel() * 2)},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "traffic": alg_bytes / launches_per_step * TRAFFIC_OVER_ALGORITHMIC,
+                     "traffic_source": "algorithmic bytes x 1.004, the ratio of dram__bytes_read.sum + dram__bytes_write.sum to "
+                                       "algorithmic bytes in profiles/quad_gemv_huffman_12288x4096_b1.md",
                      "algorithmic_bytes_per_launch": alg_bytes / launches_per_step,
                      "avg_launch_us": ms_step * 1e3 / launches_per_step,
-                     "kernel": "staged_kernel<HuffCodec, GemvSink>" if args.algo == "huffman" else "staged_kernel"},
+                     "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "kernel": ("quad_kernel<HuffCodec, B, 2> (four weight rows per warp group, one mma.sync tile per block for all rows of X)"
+                                if args.algo == "huffman" and args.tables.startswith("limit") and B > 0 else
+                                "quad_kernel / staged_kernel by table kind and batch")},
         "clocks": clocks.summary(),
     }
+    if ms_e2e is not None:
+        line["e2e"] = {"value": B / (ms_e2e / steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(x_host.numel() * 2),
+                       "d2h_bytes_per_step": int(y_host.numel() * 2)}
     if world > 1:
         line["config"]["aggregate_compressed_gbs"] = total_bytes_all_ranks / (ms_step * 1e-3) / 1e9
+        if all(hasattr(m, "local") for m in mods):
+            line["exchange_verified"] = verify_exchange(mods, meta, xs, B, world)
+    del graph
     return line, mods, meta, xs
 
 
-def dense_arm(args, dev):
-    """The same stack as plain BF16 nn.Linear layers (torch / cuBLAS), graph-replayed on the same GPU."""
+def side_run(args, rank, world, dev, **override):
+    """The same measurement with some options changed, reduced to its headline figures; frees the stack."""
+    alt = argparse.Namespace(**{**vars(args), **override})
+    other, m2, _, x2 = ours(alt, rank, world, dev, light=True)
+    del m2, x2
+    torch.cuda.empty_cache()
+    out = {"value": other["value"], "unit": "tokens/s", "ms_per_step": other["ms_per_step"], "ratio": other["config"]["ratio"],
+           "frac": other["roofline"]["frac"], "batch": other["config"]["batch"]}
+    if "exchange_verified" in other:
+        out["exchange_verified"] = other["exchange_verified"]
+    return out
+
+
+def per_shape_arm(dev, steps=5):
+    """Every Qwen3-8B linear shape x both coders on its own: graph replay over more than L2 of distinct copies."""
+    import math
+    from bf16_huffman_infer_b200 import ANSWeight, CompressedLinear, HuffmanWeight
+    peak, _ = peaks()
+    rows = []
+    for name, (M, K) in QWEN3_SHAPES.items():
+        g = torch.Generator(device=dev).manual_seed(0)
+        W = (torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        for algo, cls in (("huffman", HuffmanWeight), ("ans", ANSWeight)):
+            cw = cls.compress(W, to_cpu=False)
+            nbytes = cw.nbytes()
+            copies = max(2, math.ceil(400e6 / nbytes))
+            mods = []
+            for i in range(copies):
+                twin = cls(cw.rem.clone(), cw.exp.clone(), *[getattr(cw, k) for k in list(cw.kwargs())[2:]])
+                mods.append(CompressedLinear(twin, None))
+            for B in (1, 8):
+                x = torch.randn(B, K, device=dev).to(torch.bfloat16)
+
+                def run(mods=mods, x=x):
+                    for m in mods:
+                        m(x)
+
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side), torch.no_grad():
+                    run()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph), torch.no_grad():
+                    run()
+                for _ in range(3):
+                    graph.replay()
+                us = timed_region(graph.replay, steps, 1, dev) * 1e3 / (steps * copies)
+                alg = nbytes + B * (K + M) * 2
+                rows.append({"shape": name, "M": M, "K": K, "algo": algo, "batch": B, "us": round(us, 2),
+                             "gbs": round(alg / us / 1e3, 1), "frac": round(alg / us / 1e3 / peak, 3),
+                             "ratio": round(nbytes / (2.0 * M * K), 4)})
+                del graph
+            del mods, cw
+        del W
+        torch.cuda.empty_cache()
+    return rows
+
+
+def reference_gpu_arm(batch):
+    """The reference's own kernels (built for sm_100a, installed under baseline/_ref) in a process of their own."""
+    script = os.path.join(ROOT, "baseline", "reference_gpu_arm.py")
+    try:
+        r = subprocess.run([sys.executable, script, "--batch", str(batch)], capture_output=True, text=True, timeout=420)
+        lines = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+        if r.returncode != 0 or not lines:
+            return {"unavailable": ("exit %d: " % r.returncode + (r.stderr.strip().splitlines() or ["no output"])[-1])[:300]}
+        return json.loads(lines[-1])
+    except Exception as e:                                         # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+
+def dense_arm(args, dev, batches):
+    """The same stack as plain BF16 nn.Linear layers (torch / cuBLAS), graph-replayed on the same GPU, at every batch asked for."""
     shapes = layer_shapes(args.workload.replace("+fused", ""))      # an uncompressed model keeps its projections separate
     need = sum(m * k for _, m, k in shapes) * 2
     free, _ = torch.cuda.mem_get_info(dev)
@@ -377,31 +535,14 @@ def dense_arm(args, dev):
         with torch.no_grad():
             lin.weight.copy_((torch.randn(M, K, dtype=torch.float32, device=dev, generator=g) * 0.02).to(torch.bfloat16))
         mods.append(lin)
-    meta = [{"name": n} for n, _, _ in shapes]
-    hidden = shapes[0][2]
-    xs = {"hidden": torch.randn(args.batch, hidden, device=dev).to(torch.bfloat16)}
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side), torch.no_grad():
-        for _ in range(2):
-            run_step(mods, meta, xs, args.batch)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph), torch.no_grad():
-        run_step(mods, meta, xs, args.batch)
-    for _ in range(3):
-        graph.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_step = e0.elapsed_time(e1) / args.steps
-    return {"value": args.batch / (ms_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step, "weight_bytes": need,
-            "gbs": need / (ms_step * 1e-3) / 1e9}
+    meta = [{"name": n, "K": k} for n, _, k in shapes]
+    out = {}
+    for B in batches:
+        value, ms_step = quick_tokens_per_s(mods, meta, dev, B, args.steps)
+        out[str(B)] = {"value": value, "unit": "tokens/s", "ms_per_step": ms_step, "weight_bytes": need, "gbs": need / (ms_step * 1e-3) / 1e9}
+    del mods
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -414,17 +555,18 @@ def main():
                     help="one of %s, optionally with +fused (q/k/v and gate/up stacked into one launch each), "
                          "or layer:MxK for a single matrix, or stack:NxMxK for N distinct matrices of one shape" % sorted(WORKLOADS))
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
-    ap.add_argument("--tables", default="escape", choices=["escape", "reference"],
-                    help="Huffman table builder: 'escape' (this library's, near-entropy on every histogram) or "
-                         "'reference' (the reference's own code, bit-identical compressed bytes); both fill the "
-                         "reference's table format")
+    ap.add_argument("--tables", default="limit6", choices=["limit6", "limit8", "escape", "reference"],
+                    help="Huffman table builder: 'limit6' (the package default: codes of at most 6 bits, fastest), 'escape' "
+                         "(near-entropy on every histogram, smallest) or 'reference' (the reference's own code, bit-identical "
+                         "compressed bytes); all fill the reference's table format")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="with more than one GPU: how the row slices of every matrix are put together")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-dense", action="store_true", help="skip the uncompressed BF16 torch comparison")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-reference-tables", action="store_true",
-                    help="skip the second run with the reference's table builder")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the side measurements (other table builders, rANS, batch sweep, per-shape, reference kernels, 70B shape)")
+    ap.add_argument("--no-70b", action="store_true", help="skip the Llama-3-70B-shape stack")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -438,7 +580,7 @@ def main():
         per_step = []
         base = None
         for _ in range(max(1, min(args.steps, 3))):
-            base, step_seconds = cpu_arm(args.workload, args.algo, args.batch, budget_s=12.0)
+            base, step_seconds = cpu_arm(args.workload, args.algo, args.batch, budget_s=12.0, tables=args.tables)
             per_step.append(step_seconds)
         step_seconds = float(np.median(per_step))
         base["value"] = args.batch / step_seconds
@@ -447,7 +589,8 @@ def main():
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(per_step), "warmup": 0, "ms_per_step": step_seconds * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights, fp32 accumulate",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"{args.workload}-shape linear stack, batch {args.batch}, algo {args.algo}", "batch": args.batch, "algo": args.algo},
+            "config": {"workload": f"{args.workload}-shape linear stack, batch {args.batch}, algo {args.algo}", "batch": args.batch,
+                       "algo": args.algo, "tables": args.tables},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
@@ -463,24 +606,46 @@ def main():
     import bf16_huffman_infer_b200  # noqa: F401  (fails loudly if the native libraries are missing)
 
     line, mods, meta, xs = ours(args, rank, world, dev)
+    extras = not args.no_extras
+    qwen = args.workload.startswith("qwen3-8b")
+    if extras and world == 1:
+        # the same stack at the other batch sizes of the fused path
+        sweep = {str(args.batch): {"value": line["value"], "ms_per_step": line["ms_per_step"]}}
+        for B in (1, 2, 4, 8):
+            if str(B) not in sweep:
+                v, ms = quick_tokens_per_s(mods, meta, dev, B, max(3, args.steps // 4))
+                sweep[str(B)] = {"value": v, "ms_per_step": ms}
+        line["batch_sweep"] = sweep
     del mods, xs
     torch.cuda.empty_cache()
-    if world == 1 and args.tables == "escape" and args.algo != "ans" and not args.no_reference_tables:
-        # the same stack encoded with the reference's own table builder, timed the same way
-        free, total = torch.cuda.mem_get_info(dev)
-        if line["config"]["compressed_bytes_per_rank"] * 1.3 < free:
-            alt = argparse.Namespace(**{**vars(args), "tables": "reference"})
-            other, m2, _, x2 = ours(alt, rank, world, dev)
-            del m2, x2
-            torch.cuda.empty_cache()
-            line["reference_tables"] = {"value": other["value"], "unit": "tokens/s", "ms_per_step": other["ms_per_step"],
-                                        "ratio": other["config"]["ratio"], "roofline_frac": other["roofline"]["frac"],
-                                        "e2e": other["e2e"]["value"]}
+    if extras and world == 1 and args.algo == "huffman":
+        free, _ = torch.cuda.mem_get_info(dev)
+        if line["config"]["compressed_bytes_per_rank"] * 1.4 < free:
+            line["other_tables"] = {t: side_run(args, rank, world, dev, tables=t) for t in ("escape", "reference") if t != args.tables}
+            line["ans"] = side_run(args, rank, world, dev, algo="ans")
         else:
-            line["reference_tables"] = {"unavailable": "not enough free device memory for a second stack"}
+            line["other_tables"] = {"unavailable": "not enough free device memory for a second stack"}
+    if extras and world == 1 and qwen:
+        line["per_shape"] = per_shape_arm(dev)
+    if extras and qwen and not args.no_70b:
+        # the 70B shape the tensor-parallel configuration names, same coder and tables, rows sharded over the ranks
+        free, _ = torch.cuda.mem_get_info(dev)
+        if free > 118e9 / world + 8e9:
+            line["llama3_70b"] = side_run(args, rank, world, dev, workload="llama3-70b+fused")
+        else:
+            line["llama3_70b"] = {"unavailable": f"{free / 1e9:.0f} GB free on the device"}
     if rank == 0:
         if world == 1 and not args.no_dense:
-            line["dense_bf16_torch"] = dense_arm(args, dev)
+            batches = (1, 2, 4, 8) if "batch_sweep" in line else (args.batch,)
+            dense = dense_arm(args, dev, batches)
+            if "unavailable" in dense:
+                line["dense_bf16_torch"] = dense
+            else:
+                line["dense_bf16_torch"] = dense[str(args.batch)]
+                for B, entry in line.get("batch_sweep", {}).items():
+                    entry["dense_bf16_torch"] = dense[B]["value"]
+        if extras and world == 1 and qwen:
+            line["reference_gpu"] = reference_gpu_arm(args.batch)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch, tables=args.tables)
         print(json.dumps(line))

@@ -336,7 +336,31 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
     if (cur.valid && cur.staged) issue(cur, 0);
     else if (cur.valid) place(cur, 0);
 
-    // tables: they belong to the layer, so this still overlaps the previous kernel in the stream
+    // Everything above read weights only and is in flight (record copies, table copy).  X (and Y) belong to the
+    // previous kernel in the stream: wait for it here, and fetch the first stage of X while the tables arrive.
+    pdl_wait();
+    uint32_t launch_no = 0;
+    if (exchange) {
+        launch_no = *reinterpret_cast<const volatile uint32_t *>(peers.launches) + 1u;
+        if (blockIdx.x == 0 && tid < peers.world) red_release_sys_add(pick(peers.ready, tid), 1u);
+    }
+
+    const int64_t row_pairs = (static_cast<int64_t>(L.S) * L.Nc) >> 1;
+    auto stage_x = [&]() {
+        // A fragments: [block][pass][batch row][t] -> {pair 8j+t, pair 8j+4+t, pair 32+8j+t, pair 32+8j+4+t} of the block
+        uint4 *dst = reinterpret_cast<uint4 *>(smem + G.x_off);
+        const int total = (k_hi - k_lo) * nblk * 16 * B;
+        for (int i = tid; i < total; i += kThreads) {
+            const int tt = i & 3, rest = i >> 2;
+            const int b = rest % B, rest2 = rest / B;
+            const int j = rest2 & 3, gb = rest2 >> 2;
+            const uint32_t *s = X + b * row_pairs + (static_cast<int64_t>(k_lo) * nblk + gb) * 64 + 8 * j + tt;
+            dst[i] = make_uint4(__ldg(s), __ldg(s + 4), __ldg(s + 32), __ldg(s + 36));
+        }
+    };
+    stage_x();
+
+    // tables (their copy was started before the wait above)
     uint32_t flagged = 1u;
     const uint32_t copies = 1u << (G.copy_shift - 2);
     if (prepared == nullptr) {
@@ -372,28 +396,6 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
     }
     const bool checked = kHuff && flagged != 0u;
 
-    // Everything above read weights only.  X (and Y) belong to the previous kernel in the stream.
-    pdl_wait();
-    uint32_t launch_no = 0;
-    if (exchange) {
-        launch_no = *reinterpret_cast<const volatile uint32_t *>(peers.launches) + 1u;
-        if (blockIdx.x == 0 && tid < peers.world) red_release_sys_add(pick(peers.ready, tid), 1u);
-    }
-
-    const int64_t row_pairs = (static_cast<int64_t>(L.S) * L.Nc) >> 1;
-    auto stage_x = [&]() {
-        // A fragments: [block][pass][batch row][t] -> {pair 8j+t, pair 8j+4+t, pair 32+8j+t, pair 32+8j+4+t} of the block
-        uint4 *dst = reinterpret_cast<uint4 *>(smem + G.x_off);
-        const int total = (k_hi - k_lo) * nblk * 16 * B;
-        for (int i = tid; i < total; i += kThreads) {
-            const int tt = i & 3, rest = i >> 2;
-            const int b = rest % B, rest2 = rest / B;
-            const int j = rest2 & 3, gb = rest2 >> 2;
-            const uint32_t *s = X + b * row_pairs + (static_cast<int64_t>(k_lo) * nblk + gb) * 64 + 8 * j + tt;
-            dst[i] = make_uint4(__ldg(s), __ldg(s + 4), __ldg(s + 32), __ldg(s + 36));
-        }
-    };
-
     float c[PPW][4];
 #pragma unroll
     for (int pp = 0; pp < PPW; pp++) c[pp][0] = c[pp][1] = c[pp][2] = c[pp][3] = 0.f;
@@ -410,7 +412,7 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
             if (cur.valid && cur.staged) issue(cur, slot);
             else if (cur.valid) place(cur, slot);
         }
-        stage_x();
+        if (stage > 0) stage_x();
         __syncthreads();
 
         uint32_t r_cur[PPW][kRG], r_nxt[PPW][kRG];

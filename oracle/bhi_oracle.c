@@ -361,6 +361,15 @@ int bhi_oracle_gemv(int algo, const uint8_t *rem, const uint32_t *exp, int64_t e
     return 0;
 }
 
+/* Worker threads of the following calls (the benchmark sets it to the cores it may use, whatever OMP_NUM_THREADS says). */
+void bhi_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int bhi_oracle_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -52,6 +52,12 @@ def threads() -> int:
     return int(lib().bhi_oracle_threads())
 
 
+def set_threads(n: int) -> int:
+    """Use ``n`` worker threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1); returns the count in effect."""
+    lib().bhi_oracle_set_threads(C.c_int(int(n)))
+    return threads()
+
+
 def chunk_count(k: int) -> int:
     return int(lib().bhi_oracle_chunk_count(C.c_int(k)))
 
