@@ -302,8 +302,8 @@ struct DenseSink {
 //   ready  - each rank adds 1 on every peer when its launch may be written to (its earlier consumers of
 //            Y are done: the add comes after the wait for the previous kernel in the stream); a warp
 //            checks its own copy (>= world * launch number) before its first remote store;
-//   arrive (local) - every CTA adds 1 after its stores; the CTA that brings it to grid * launch number is
-//            the last one of this launch on this GPU;
+//   arrive (local) - every CTA adds 1 after its stores; the CTA that brings it to the grid size is the last
+//            one of this launch on this GPU and puts it back to zero;
 //   done   - that last CTA adds 1 on every peer (release at system scope, cumulative over all CTAs'
 //            stores through the arrive counter) and then waits until its own copy shows
 //            world * launch number, so whatever runs next on the stream sees the whole of Y.  One
@@ -380,7 +380,10 @@ __device__ __forceinline__ void exchange_finish(const PeerSet &peers, uint32_t l
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t before = atom_add_acq_rel_gpu(peers.launches + 1, 1u);
-        if (before + 1u == launch_no * gridDim.x) {
+        if (before + 1u == gridDim.x) {
+            // last CTA of this launch.  The arrival counter goes back to zero for the next launch of the layer,
+            // whatever grid that one uses (its CTAs arrive only after this whole grid has completed).
+            *reinterpret_cast<volatile uint32_t *>(peers.launches + 1) = 0u;
 #pragma unroll
             for (int q = 0; q < kMaxPeers; q++)
                 if (q < peers.world) red_release_sys_add(peers.done[q], 1u);
