@@ -246,15 +246,6 @@ int bhi_debug_status(int *status_out) {
     return BHI_OK;
 }
 
-#ifdef BHI_TRACE
-// debug builds only: copy the per-warp timeline to the host
-int bhi_debug_trace(long long *out, int count) {
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * count);
-    return e == cudaSuccess ? BHI_OK : cuda_fail(e, "trace read");
-}
-#endif
-
 int bhi_gemv_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
                           const uint16_t *X, uint16_t *Y, const int32_t *offsets,
                           const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,

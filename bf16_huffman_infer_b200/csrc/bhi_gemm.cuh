@@ -39,15 +39,6 @@
 
 namespace bhi {
 
-// timeline of the first 64 blocks of CTA 0, warps 0 and 7 (builds with -DBHI_TRACE only)
-#ifdef BHI_TRACE
-#define GEMM_TRACE(i)                                                                                     \
-    do { if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 7) && block_no < 64u)                          \
-        g_trace[((warp ? 1 : 0) * 64 + block_no) * 8 + (i)] = clock64(); } while (0)
-#else
-#define GEMM_TRACE(i) do {} while (0)
-#endif
-
 constexpr int kGemmWarps = 32;
 constexpr int kGemmRows = 32;                    // weight rows per set (MMA N)
 constexpr int kGemmBatch = 128;                  // MMA M
@@ -341,7 +332,6 @@ gemm_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
 
             auto step = [&](int blk, uint32_t r) {
                 const int gblk = kk * nblk + blk;
-                GEMM_TRACE(0);
                 uint32_t w0 = 0u, w1 = 0u;
                 if (fast_path) {
                     uint32_t e0, e1;
@@ -356,18 +346,15 @@ gemm_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                     w1 = join_pair<1>(r, e.y);
                 }
 
-                GEMM_TRACE(1);
                 // the stage is free once the MMAs that read it NS blocks ago have completed
                 if (wraps > 0u && !mbar_wait_bounded(empty_bar + 8u * stage, (wraps - 1u) & 1u) && lane == 0)
                     atomicExch(&g_staged_status, 3);
-                GEMM_TRACE(2);
                 uint8_t *ws = smem + ws0 + stage * kWTileBytes;
                 *reinterpret_cast<uint32_t *>(ws) = w0;
                 *reinterpret_cast<uint32_t *>(ws + 8 * kWLbo * 16) = w1;
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_bar + 8u * stage);
-                GEMM_TRACE(3);
                 // Blocks take turns in who issues: the issuing lane stalls while the tensor pipe works off the
                 // previous block, and this spreads that stall over all warps.  The MMAs of block t are issued
                 // before those of block t + 1 because their issuer arrives on block t + 1's barrier afterwards.
@@ -380,9 +367,7 @@ gemm_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                             if (!mbar_wait_bounded(empty_bar + 8u * ps, pw & 1u)) atomicExch(&g_staged_status, 6);
                             request_x(block_no - 1u + P.stages);
                         }
-                        GEMM_TRACE(4);
                         if (!mbar_wait_bounded(full_bar + 8u * stage, wraps & 1u)) atomicExch(&g_staged_status, 4);
-                        GEMM_TRACE(5);
                         tc_fence_after();
                         const uint32_t xt = smem_base + P.x_off + stage * P.x_stage, wt = smem_base + P.w_off + stage * kWTileBytes;
 #pragma unroll
@@ -392,7 +377,6 @@ gemm_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                         umma_commit(empty_bar + 8u * stage);
                         if (kk == L.S - 1 && blk == nblk - 1) umma_commit(done_bar + 8u * (nset & 1u));
                         tc_fence_before();
-                        GEMM_TRACE(6);
                     }
                     __syncwarp();
                 }

@@ -90,18 +90,6 @@ static_assert(sizeof(HuffTables) <= kExactBytes && sizeof(AnsTables) <= kExactBy
 
 __device__ int g_staged_status = 0;            // 0 = fine; otherwise the last failure code
 
-// Optional per-warp timeline (compile with -DBHI_TRACE): slot i of warp w of CTA c holds the SM
-// clock at trace point i.  Off in normal builds.
-#ifdef BHI_TRACE
-constexpr int kTraceSlots = 8;
-__device__ long long g_trace[160 * 32 * kTraceSlots];
-#define BHI_TRACE_POINT(i)                                                                          \
-    do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 160)                                              \
-        g_trace[(blockIdx.x * 32 + (threadIdx.x >> 5)) * kTraceSlots + (i)] = clock64(); } while (0)
-#else
-#define BHI_TRACE_POINT(i) do {} while (0)
-#endif
-
 // ---- PTX wrappers ----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -662,8 +650,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     const int nblk = L.Nc >> 7;
     const int rows_cta = row_hi - row_lo;
     const int slots = split ? L.S : 1;             // partial sums kept per row when results are staged
-
-    BHI_TRACE_POINT(0);
     pdl_launch_dependents();
     // The first row of every warp is fixed (row_lo + warp), so its sign/mantissa row can be
     // requested from HBM before anything else is known; later rows come from the shared counter.
@@ -729,8 +715,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     cur.valid = false;
     unit_at(warp, cur);
     if (cur.valid && cur.staged) issue(cur, 0);
-
-    BHI_TRACE_POINT(1);
     // Tables first: they belong to the layer, so this still overlaps the previous kernel in the stream
     // (and the first record copy in flight).
     Sink sink = sink_proto;
@@ -758,8 +742,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
     sink.after_wait(lane);
     sink.stage(smem + kHeaderBytes, threadIdx.x, blockDim.x);
     __syncthreads();
-
-    BHI_TRACE_POINT(2);
     sink.reset(lane);
     int slot = 0;
     uint32_t phases = 0u;                          // bit s = parity the next wait on slot s expects
@@ -786,7 +768,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
             }
             const bool arrived = mbar_wait_bounded(bar0 + 8u * slot, (phases >> slot) & 1u);
             phases ^= 1u << slot;
-            BHI_TRACE_POINT(cur.k == 0 && have_first == false ? 3 : 5);
             if (arrived) {
                 Dec dec;
                 // cursors may not pass the last word row that is still inside this CTA's shared memory window
@@ -835,7 +816,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
                 sink.put(k, gblk0 + blk, join_pair<0>(r, (a0 << 7) | (a1 << 23)), join_pair<1>(r, (b0 << 7) | (b1 << 23)));
             }
         }
-        BHI_TRACE_POINT(have_first ? 6 : 4);
         have_first = next_first;
         if (kPart) {
             if (split || cur.k == L.S - 1) sink.finish_part(part, cur.m - row_lo, split ? cur.k : 0, rows_cta, slots, lane);
@@ -852,7 +832,6 @@ staged_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, Sink
         sink.combine(part, row_lo, rows_cta, slots, lane);
     }
     sink.finish_kernel();
-    BHI_TRACE_POINT(7);
 }
 
 // ---- host side -------------------------------------------------------------------------------------

@@ -43,15 +43,16 @@ def build(arch: str, layers: int | None, dev: torch.device):
 
 
 def decode_speed(model, cfg, batch: int, prompt: int, tokens: int, dev: torch.device):
-    """tokens/s of a greedy loop over the graphed one-token step, and of ``generate`` (which adds Hugging
-    Face's per-token host work), prompt processing excluded from both; plus the generated ids."""
+    """tokens/s of a greedy loop over the graphed one-token step, and of ``generate`` (the same graph replays plus
+    Hugging Face's per-token host work), prompt processing excluded from both; plus the generated ids and how
+    many one-token steps were graph replays / eager."""
     from transformers import StaticCache
     from .. import get_graphed_model
     cache = StaticCache(config=cfg, max_cache_len=prompt + tokens + 8)
     graphed = get_graphed_model(model, cache)
     ids = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=torch.Generator().manual_seed(0)).to(dev)
     kw = dict(do_sample=False)
-    graphed.generate(ids, max_new_tokens=4, min_new_tokens=4, **kw)                  # captures the step graph
+    graphed.generate(ids, max_new_tokens=4, min_new_tokens=4, **kw)                  # the first one-token step captures the graph
     torch.cuda.synchronize()
 
     def timed(n):
@@ -76,7 +77,7 @@ def decode_speed(model, cfg, batch: int, prompt: int, tokens: int, dev: torch.de
         e1.record()
         torch.cuda.synchronize()
     step_tps = batch * (tokens - 1) / (e0.elapsed_time(e1) * 1e-3)
-    return step_tps, generate_tps, out
+    return step_tps, generate_tps, out, dict(graphed.graph_stats)
 
 
 def main():
@@ -87,7 +88,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
-    ap.add_argument("--tables", default="escape", choices=["escape", "reference"])
+    ap.add_argument("--tables", default="limit6", choices=["limit6", "limit8", "escape", "reference"])
     ap.add_argument("--min-out-features", type=int, default=0)
     ap.add_argument("--no-fuse", action="store_true", help="keep q/k/v and gate/up as separate layers")
     args = ap.parse_args()
@@ -96,7 +97,7 @@ def main():
     dev = torch.device("cuda", 0)
     cfg, model = build(args.arch, args.layers, dev)
     size_raw = get_model_size(model)
-    dense_tps, dense_gen_tps, dense_ids = decode_speed(model, cfg, args.batch, args.prompt, args.tokens, dev)
+    dense_tps, dense_gen_tps, dense_ids, _ = decode_speed(model, cfg, args.batch, args.prompt, args.tokens, dev)
     t0 = time.perf_counter()
     convert_all_linear(model, min_out_features=args.min_out_features, progress=False, algo=args.algo,
                        fuse_siblings=not args.no_fuse, huffman_tables=args.tables)
@@ -104,7 +105,7 @@ def main():
     torch.cuda.synchronize()
     convert_s = time.perf_counter() - t0
     size_comp = get_model_size(model)
-    comp_tps, comp_gen_tps, comp_ids = decode_speed(model, cfg, args.batch, args.prompt, args.tokens, dev)
+    comp_tps, comp_gen_tps, comp_ids, stats = decode_speed(model, cfg, args.batch, args.prompt, args.tokens, dev)
     same = int((dense_ids == comp_ids).all())
     first_diff = None if same else int((dense_ids != comp_ids).any(0).nonzero()[0])
     print(json.dumps({
@@ -113,6 +114,7 @@ def main():
         "fused_siblings": not args.no_fuse,
         "dense_bf16_tokens_per_s": round(dense_tps, 1), "compressed_tokens_per_s": round(comp_tps, 1),
         "through_generate": {"dense_bf16_tokens_per_s": round(dense_gen_tps, 1), "compressed_tokens_per_s": round(comp_gen_tps, 1)},
+        "one_token_steps": stats,
         "model_bytes_bf16": size_raw, "model_bytes_compressed": size_comp, "ratio": round(size_comp / size_raw, 4),
         "convert_seconds": round(convert_s, 1),
         # lossless weights, but the fused kernel sums in another order than cuBLAS: greedy tokens of a random-weight
