@@ -21,7 +21,7 @@ Printed JSON line (rank 0):
            bounded sample of the same workload;
   other_tables  (one GPU, Huffman) the same stack encoded with the other table builders ("escape": smallest;
            "reference": the reference's own, byte-identical buffers), timed the same way;
-  ans      the same stack with the rANS coder;
+  ans      the same stack with the rANS coder at 8 (the reference's), 10 and 12 probability bits;
   batch_sweep  tokens/s of the same stack at batch 1, 2, 4, 8 with the uncompressed torch stack beside each;
   per_shape  every Qwen3-8B linear shape x both coders on its own: time per launch over more than L2 of distinct
            copies, compressed GB/s, fraction of the measured HBM peak;
@@ -165,7 +165,7 @@ class ClockSampler:
 
 
 # ---- the CPU arm (oracle): bounded sample of the workload ------------------------------------------------
-def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference"):
+def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference", ans_precision=8):
     """Times the CPU restatement of the fused path on the first matrices of the stack, in model order,
     until about `budget_s` seconds of CPU work have been measured, and scales to a whole step by
     weight count."""
@@ -182,7 +182,7 @@ def cpu_arm(workload, algo, batch, budget_s=12.0, tables="reference"):
             enc.build_lut(hist, method=tables)
             return {"LUT1": enc.LUT1, "LUT2": enc.LUT2, "LUT3": enc.LUT3, "LUT4": enc.LUT4,
                     "code_lengths": enc.code_lengths, "code_values": enc.code_values}
-        enc = RANSEncoder([int(v) for v in hist], precision=8)
+        enc = RANSEncoder([int(v) for v in hist], precision=ans_precision)
         lut = np.array([(s << 24) | (f << 12) | r for s, f, r in enc.decode_lut], dtype=np.uint32)
         return {"freq": np.array(enc.freq, np.uint32), "cum": np.array(enc.cum, np.uint32), "LUT": lut.view(np.int32)}
 
@@ -368,10 +368,11 @@ def verify_exchange(mods, meta, xs, B, world):
 
 def ours(args, rank, world, dev, light=False):
     """Builds and times one stack.  light=True: device-resident timing only (for the side runs)."""
-    from bf16_huffman_infer_b200 import set_huffman_tables
+    from bf16_huffman_infer_b200 import set_ans_precision, set_huffman_tables
 
     t_setup = time.time()
     set_huffman_tables(args.tables)
+    set_ans_precision(args.ans_precision)
     mods, meta = build_stack(args.workload, args.algo, rank, world, dev, exchange=args.exchange)
     hidden = meta[0]["K"]
     B = args.batch
@@ -416,7 +417,7 @@ def ours(args, rank, world, dev, light=False):
             "workload": f"{args.workload}-shape linear stack ({len(mods)} matrices, {sum(m['M'] * m['K'] for m in meta) / 1e9:.2f}G weights), "
                         f"batch {B}, algo {args.algo}"
                         + (f" ({args.tables} table builder)" if args.algo != "ans" else "") + f", rows sharded over {world} GPU(s)",
-            "batch": B, "algo": args.algo, "tables": args.tables, "l2": "inputs larger than L2 (the step streams every compressed weight once)",
+            "batch": B, "algo": args.algo, "tables": args.tables if args.algo != "ans" else f"{args.ans_precision}-bit model", "l2": "inputs larger than L2 (the step streams every compressed weight once)",
             "compressed_bytes_per_rank": int(sum(m["bytes"] for m in meta)),
             "ratio": sum(m["bytes"] for m in meta) / (2.0 * sum(m["local_rows"] * m["K"] for m in meta)),
             "setup_s": round(setup_s, 1),
@@ -555,6 +556,7 @@ def main():
                     help="one of %s, optionally with +fused (q/k/v and gate/up stacked into one launch each), "
                          "or layer:MxK for a single matrix, or stack:NxMxK for N distinct matrices of one shape" % sorted(WORKLOADS))
     ap.add_argument("--algo", default="huffman", choices=["huffman", "ans", "smallest"])
+    ap.add_argument("--ans-precision", type=int, default=8, choices=[8, 9, 10, 11, 12], help="probability bits of the rANS model")
     ap.add_argument("--tables", default="limit6", choices=["limit6", "limit8", "escape", "reference"],
                     help="Huffman table builder: 'limit6' (the package default: codes of at most 6 bits, fastest), 'escape' "
                          "(near-entropy on every histogram, smallest) or 'reference' (the reference's own code, bit-identical "
@@ -580,7 +582,7 @@ def main():
         per_step = []
         base = None
         for _ in range(max(1, min(args.steps, 3))):
-            base, step_seconds = cpu_arm(args.workload, args.algo, args.batch, budget_s=12.0, tables=args.tables)
+            base, step_seconds = cpu_arm(args.workload, args.algo, args.batch, budget_s=12.0, tables=args.tables, ans_precision=args.ans_precision)
             per_step.append(step_seconds)
         step_seconds = float(np.median(per_step))
         base["value"] = args.batch / step_seconds
@@ -622,7 +624,8 @@ def main():
         free, _ = torch.cuda.mem_get_info(dev)
         if line["config"]["compressed_bytes_per_rank"] * 1.4 < free:
             line["other_tables"] = {t: side_run(args, rank, world, dev, tables=t) for t in ("escape", "reference") if t != args.tables}
-            line["ans"] = side_run(args, rank, world, dev, algo="ans")
+            # rANS: the reference's 8-bit probabilities and the finer models its table word allows
+            line["ans"] = {str(p): side_run(args, rank, world, dev, algo="ans", ans_precision=p) for p in (8, 10, 12)}
         else:
             line["other_tables"] = {"unavailable": "not enough free device memory for a second stack"}
     if extras and world == 1 and qwen:
@@ -647,7 +650,7 @@ def main():
         if extras and world == 1 and qwen:
             line["reference_gpu"] = reference_gpu_arm(args.batch)
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch, tables=args.tables)
+            line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch, tables=args.tables, ans_precision=args.ans_precision)
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

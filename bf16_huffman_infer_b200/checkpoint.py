@@ -29,7 +29,10 @@ _FORMAT = "bf16_huffman_infer_b200/1"
 
 
 def _weight_meta(w: HuffmanWeight) -> Dict:
-    return {"algo": w.algo, "rem": list(w.rem.shape), "exp": int(w.exp.numel()), "offsets": list(w.offsets.shape)}
+    meta = {"algo": w.algo, "rem": list(w.rem.shape), "exp": int(w.exp.numel()), "offsets": list(w.offsets.shape)}
+    if w.algo == "ans":
+        meta["lut"] = int(w.LUT.numel())        # 2^precision table words
+    return meta
 
 
 def compressed_manifest(model: nn.Module) -> Dict:
@@ -68,7 +71,8 @@ def _validate(model: nn.Module, manifest: Dict) -> None:
         rem = meta.get("rem")
         if (meta.get("algo") not in ("huffman", "ans") or not isinstance(rem, list) or len(rem) != 3
                 or rem[1] != out_features or rem[0] * rem[2] != in_features
-                or meta.get("offsets") != [rem[0], rem[1]] or not isinstance(meta.get("exp"), int) or meta["exp"] < 64):
+                or meta.get("offsets") != [rem[0], rem[1]] or not isinstance(meta.get("exp"), int) or meta["exp"] < 64
+                or meta.get("lut", 256) not in (256, 512, 1024, 2048, 4096)):
             raise ValueError(f"checkpoint entry {name!r} does not fit a linear layer {in_features} -> {out_features}: {meta}")
 
     names = dict(model.named_modules())
@@ -99,7 +103,7 @@ def _empty_weight(meta: Dict) -> HuffmanWeight:
     exp = torch.empty(meta["exp"], dtype=torch.int32)
     offsets = torch.empty(meta["offsets"], dtype=torch.int32)
     if meta["algo"] == "ans":
-        return ANSWeight(rem, exp, offsets, torch.empty(256, dtype=torch.int32))
+        return ANSWeight(rem, exp, offsets, torch.empty(int(meta.get("lut", 256)), dtype=torch.int32))
     tables = [torch.empty(256, dtype=torch.uint8) for _ in range(5)]
     return HuffmanWeight(rem, exp, offsets, *tables)
 

@@ -219,7 +219,7 @@ using namespace bhi;
 extern "C" {
 
 const char *bhi_last_error(void) { return g_error.c_str(); }
-int bhi_abi_version(void) { return 1; }
+int bhi_abi_version(void) { return 2; }
 int bhi_set_kernel_path(int path) { return g_path.exchange(path); }
 int bhi_set_launch_overlap(int on) { return g_overlap.exchange(on ? 1 : 0); }
 int bhi_set_quad_warps(int warps) {
@@ -332,12 +332,13 @@ int bhi_linear_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp
 }
 
 int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                         int split_k, int M, int Nc, int batch, void *stream) {
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    BHI_REQUIRE(precision >= BHI_ANS_PRECISION && precision <= BHI_ANS_MAX_PRECISION, "rANS precision must be in [8, 12]");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    AnsArgs t{LUT};
+    AnsArgs t{LUT, precision};
     return run_linear<AnsCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
 
@@ -380,32 +381,35 @@ int bhi_gemv_bf16_huffman_exchange_static(const uint8_t *A_rem, const uint32_t *
 }
 
 int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT,
+                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT, int precision,
                                int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream) {
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    BHI_REQUIRE(precision >= BHI_ANS_PRECISION && precision <= BHI_ANS_MAX_PRECISION, "rANS precision must be in [8, 12]");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    AnsArgs t{LUT};
+    AnsArgs t{LUT, precision};
     return run_exchange<AnsCodec>(L, t, nullptr, X, batch, exchange, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                       int split_k, int M, int Nc, int batch, void *stream) {
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    BHI_REQUIRE(precision >= BHI_ANS_PRECISION && precision <= BHI_ANS_MAX_PRECISION, "rANS precision must be in [8, 12]");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    AnsArgs t{LUT};
+    AnsArgs t{LUT, precision};
     return run_gemv<AnsCodec>(L, t, nullptr, X, Y, batch, static_cast<cudaStream_t>(stream));
 }
 
 int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                    int split_k, int M, int Nc, void *stream) {
     if (int rc = check_layer(A_rem, A_exp, exp_words, offsets, split_k, M, Nc)) return rc;
     BHI_REQUIRE(LUT && aligned(LUT, 4), "null or unaligned table");
+    BHI_REQUIRE(precision >= BHI_ANS_PRECISION && precision <= BHI_ANS_MAX_PRECISION, "rANS precision must be in [8, 12]");
     Layer L{A_rem, A_exp, exp_words, offsets, split_k, M, Nc};
-    AnsArgs t{LUT};
+    AnsArgs t{LUT, precision};
     return run_decode<AnsCodec>(L, t, nullptr, Y, static_cast<cudaStream_t>(stream));
 }
 

@@ -11,8 +11,8 @@
 
 namespace bhi {
 
-constexpr int kAnsBits = BHI_ANS_PRECISION;
-constexpr uint32_t kAnsMask = (1u << kAnsBits) - 1;
+constexpr int kAnsBitsMin = 8;                    // probability precision of an rANS table: 2^bits slots
+constexpr int kAnsBitsMax = BHI_ANS_MAX_PRECISION;
 constexpr int kStreamsPerRecord = 64;   // 2 per lane: stream lane (first 64 columns of a block) and lane+32
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -119,17 +119,23 @@ struct HuffStream {
 };
 
 // rANS: one table word per slot = sym<<24 | freq<<12 | (slot - cum[sym]), reference
-// src/kernel.cu:647-683.
+// src/kernel.cu:647-683.  The table has 2^bits slots (the reference fixes bits = 8; its word layout and
+// its static_assert allow up to 12).  The table-exact decoder reads the caller's table in global memory.
 struct AnsTables {
-    uint32_t slot[1 << kAnsBits];
+    const uint32_t *lut;
+    uint32_t bits;
 };
 
 struct AnsArgs {
     const uint32_t *lut;
+    int bits;
 };
 
-__device__ __forceinline__ void load_tables(AnsTables &t, const AnsArgs &a, int tid, int nthreads) {
-    for (int i = tid; i < (1 << kAnsBits); i += nthreads) t.slot[i] = a.lut[i];
+__device__ __forceinline__ void load_tables(AnsTables &t, const AnsArgs &a, int tid, int) {
+    if (tid == 0) {
+        t.lut = a.lut;
+        t.bits = static_cast<uint32_t>(a.bits);
+    }
 }
 
 template <class Words>
@@ -138,12 +144,16 @@ struct AnsStream {
     uint64_t state;
     __device__ __forceinline__ void init(const Words &w) { src = w; state = src.pop(); }
     __device__ __forceinline__ uint32_t next(const AnsTables &t) {
-        if (state < (1u << kAnsBits)) state = (state << 32) | src.pop();
-        uint32_t e = t.slot[static_cast<uint32_t>(state) & kAnsMask];
-        state = static_cast<uint64_t>((e >> 12) & 0xFFFu) * (state >> kAnsBits) + (e & 0xFFFu);
+        if (state < (1ull << t.bits)) state = (state << 32) | src.pop();
+        uint32_t e = __ldg(t.lut + (static_cast<uint32_t>(state) & ((1u << t.bits) - 1u)));
+        state = static_cast<uint64_t>((e >> 12) & 0xFFFu) * (state >> t.bits) + (e & 0xFFFu);
         return e >> 24;
     }
 };
+
+// probability precision carried by a codec's table arguments (Huffman: unused)
+__host__ __device__ inline uint32_t ans_bits_of(const HuffArgs &) { return kAnsBitsMin; }
+__host__ __device__ inline uint32_t ans_bits_of(const AnsArgs &a) { return static_cast<uint32_t>(a.bits); }
 
 struct HuffCodec {
     using Tables = HuffTables;

@@ -30,14 +30,20 @@ __global__ void huffman_encode_chars_kernel(const uint8_t *__restrict__ data, in
     out_len[t] = cnt;
 }
 
+// Probability precision of an rANS model: its frequencies sum to 2^bits (cum[255] + freq[255] is that sum).
+__device__ __forceinline__ uint32_t ans_model_bits(const uint32_t *sf, const uint32_t *sc) {
+    const uint32_t total = sc[255] + sf[255];
+    return total ? 31u - static_cast<uint32_t>(__clz(total)) : kAnsBitsMin;
+}
+
 // rANS step shared by all encoders: emits renormalisation words through `put(word)`.
 template <class Put>
-__device__ __forceinline__ void ans_push(uint64_t &state, uint32_t f, uint32_t c, Put &&put) {
+__device__ __forceinline__ void ans_push(uint64_t &state, uint32_t f, uint32_t c, uint32_t bits, Put &&put) {
     while ((state >> 32) >= f) {
         put(static_cast<uint32_t>(state));
         state >>= 32;
     }
-    state = ((state / f) << kAnsBits) + (state % f) + c;
+    state = ((state / f) << bits) + (state % f) + c;
 }
 
 __global__ void ans_encode_words_kernel(const uint8_t *__restrict__ data, int streams, int n,
@@ -50,10 +56,11 @@ __global__ void ans_encode_words_kernel(const uint8_t *__restrict__ data, int st
     if (t >= streams) return;
     const uint8_t *src = data + static_cast<int64_t>(t) * n;
     uint32_t *dst = out + static_cast<int64_t>(t) * n * 8;
-    uint64_t state = 1u << kAnsBits;
+    const uint32_t bits = ans_model_bits(sf, sc);
+    uint64_t state = 1ull << bits;
     int32_t cnt = 0;
     auto put = [&](uint32_t w) { dst[cnt++] = w; };
-    for (int i = n - 1; i >= 0; i--) ans_push(state, sf[src[i]], sc[src[i]], put);
+    for (int i = n - 1; i >= 0; i--) ans_push(state, sf[src[i]], sc[src[i]], bits, put);
     while (state > 0) { put(static_cast<uint32_t>(state)); state >>= 32; }
     for (int i = 0; i < cnt / 2; i++) {
         const uint32_t a = dst[i];
@@ -161,12 +168,13 @@ huffman_emit_kernel(EncGeom g, const uint8_t *__restrict__ code_len, const uint3
 template <class Put>
 __device__ __forceinline__ void ans_encode_record_stream(const EncGeom &g, int k, int m, int st,
                                                          const uint32_t *sf, const uint32_t *sc, Put &&put) {
-    uint64_t state = 1u << kAnsBits;
+    const uint32_t bits = ans_model_bits(sf, sc);
+    uint64_t state = 1ull << bits;
     for (int blk = (g.Nc >> 7) - 1; blk >= 0; blk--) {
         const uint32_t p = enc_pair(g, k, m, st, blk);
         const uint32_t e1 = exp_hi(p), e0 = exp_lo(p);
-        ans_push(state, sf[e1], sc[e1], put);
-        ans_push(state, sf[e0], sc[e0], put);
+        ans_push(state, sf[e1], sc[e1], bits, put);
+        ans_push(state, sf[e0], sc[e0], bits, put);
     }
     while (state > 0) { put(static_cast<uint32_t>(state)); state >>= 32; }
 }

@@ -104,7 +104,10 @@ __device__ __forceinline__ void gemm_fast_table(uint32_t *fast, const HuffTables
     }
 }
 __device__ __forceinline__ void gemm_fast_table(uint32_t *fast, const AnsTables &t, int tid, int n) {
-    for (int i = tid; i < (1 << kAnsBits); i += n) *reinterpret_cast<uint2 *>(fast + i * kGemmCopies) = make_uint2(t.slot[i], t.slot[i]);
+    for (int i = tid; i < (1 << t.bits); i += n) {
+        const uint32_t e = __ldg(t.lut + i);
+        *reinterpret_cast<uint2 *>(fast + i * kGemmCopies) = make_uint2(e, e);
+    }
 }
 
 // A record that cannot be staged (too large for the ring, or offsets out of storage order) is decoded
@@ -506,7 +509,8 @@ static int gemm_launch(const Layer &L, const typename Codec::Args &targs, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
-    const Consts k{1u, 8u, 4u * kGemmCopies, 65536u};
+    const uint32_t ans_bits = ans_bits_of(targs);
+    const Consts k{ans_bits, (1u << ans_bits) - 1u, 1u, 8u, 4u * kGemmCopies, 65536u};
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, xmap, Y, B, plan, k);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "fused tensor-core kernel launch");
 }

@@ -158,13 +158,13 @@ struct QuadHuff {
 struct QuadAnsLane {
     uint32_t lo, hi, nx;
     __device__ __forceinline__ uint32_t symbol(const QuadCtx &c, uint32_t alim) {
-        if (hi == 0 && lo < (1u << kAnsBits)) {
+        if (hi == 0 && lo <= c.k.ans_mask) {
             hi = lo;
             lo = lds32(c.smem, nx);
             nx = min(nx + 256u, alim);
         }
         const uint32_t e = lds32(c.smem, ((lo << c.copy_shift) & c.index_mask) | c.copy_off);
-        const uint32_t shifted = __funnelshift_r(lo, hi, kAnsBits);
+        const uint32_t shifted = __funnelshift_r(lo, hi, c.k.ans_bits);
         const uint64_t next = static_cast<uint64_t>((e >> 12) & 0xFFFu) * shifted + (e & 0xFFFu);
         lo = static_cast<uint32_t>(next);
         hi = static_cast<uint32_t>(next >> 32);
@@ -372,8 +372,8 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
                 for (uint32_t c = 0; c < copies; c++) fast[v * copies + c] = e;
             }
         } else {
-            for (int v = tid; v < (1 << kAnsBits); v += kThreads) {
-                const uint32_t e = tab.slot[v];
+            for (int v = tid; v < (1 << kc.ans_bits); v += kThreads) {
+                const uint32_t e = __ldg(targs.lut + v);
                 for (uint32_t c = 0; c < copies; c++) fast[v * copies + c] = e;
             }
         }
@@ -573,9 +573,9 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
 // ---- host side -------------------------------------------------------------------------------------
 // Shared-memory plan of a launch; false when the shape does not fit (the caller then uses another kernel).
 template <class Codec, int B>
-static bool quad_plan(const Layer &L, int grid, bool exchange, QuadGeom &G, uint32_t &smem_bytes) {
+static bool quad_plan(const Layer &L, int grid, bool exchange, uint32_t ans_bits, QuadGeom &G, uint32_t &smem_bytes) {
     constexpr bool kHuff = std::is_same<Codec, HuffCodec>::value;
-    const uint32_t one_table = kHuff ? kPairEntries * 4u : (4u << kAnsBits);
+    const uint32_t one_table = kHuff ? kPairEntries * 4u : (4u << ans_bits);
     const uint32_t chunk_bytes = static_cast<uint32_t>(B) * L.Nc * 2u;
     const int nquads = (L.M + 3) / 4;
     const int nq = (nquads + grid - 1) / grid;
@@ -603,7 +603,7 @@ static bool quad_plan(const Layer &L, int grid, bool exchange, QuadGeom &G, uint
         if (ring_bytes > 4u * kRingMax) ring_bytes = 4u * kRingMax;
         G.lut_bytes = lut;
         G.copy_shift = 2u + copies_log2;
-        G.index_mask = kHuff ? (static_cast<uint32_t>(kPairEntries - 1) << G.copy_shift) : (kAnsMask << G.copy_shift);
+        G.index_mask = kHuff ? (static_cast<uint32_t>(kPairEntries - 1) << G.copy_shift) : (((1u << ans_bits) - 1u) << G.copy_shift);
         G.part_off = lut + kExactBytes + kQuadCtrlBytes;
         G.acc_off = G.part_off + kQuadPartBytes;
         G.ys_off = G.acc_off + acc_bytes;
@@ -629,7 +629,7 @@ static int quad_launch_p(const Layer &L, const typename Codec::Args &targs, cons
     if (grid > nquads) grid = nquads;
     QuadGeom G{};
     uint32_t smem_bytes = 0;
-    if (!quad_plan<Codec, B>(L, grid, peers != nullptr, G, smem_bytes)) return kStagedDeclined;
+    if (!quad_plan<Codec, B>(L, grid, peers != nullptr, ans_bits_of(targs), G, smem_bytes)) return kStagedDeclined;
     auto kernel = quad_kernel<Codec, B, PPW>;
     if (int rc = staged_prepare(kernel)) return rc;
     PeerSet ps{};
@@ -644,7 +644,8 @@ static int quad_launch_p(const Layer &L, const typename Codec::Args &targs, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
-    const Consts k{1u, 8u, 4u * kCopies, 65536u};
+    const uint32_t ans_bits = ans_bits_of(targs);
+    const Consts k{ans_bits, (1u << ans_bits) - 1u, 1u, 8u, 4u * kCopies, 65536u};
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, reinterpret_cast<const uint32_t *>(X), Y, ps, G, k);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "quad kernel launch");
 }

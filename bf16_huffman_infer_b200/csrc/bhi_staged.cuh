@@ -23,7 +23,7 @@
 //
 // Decode plan (rANS).  One table word per slot, 64-bit state kept as two registers,
 // state' = freq * (state >> 8) + rem as one 32x32+64 multiply-add (a valid stream keeps
-// state < 2^40), refill word fetched from the ring.
+// state < 2^(32 + bits), bits <= 12), refill word fetched from the ring.
 //
 // Multiply-accumulate (GEMV sinks).  One mma.sync.m16n8k16 per block and pair of batch rows, with the
 // words a lane has just rebuilt as its B fragment and its own X pairs as its A fragment; see the
@@ -79,6 +79,7 @@ constexpr uint32_t kRemMask = 0x807F807Fu;     // sign + mantissa bits of a bf16
 // shifts/adds on the (half-rate, saturated) integer pipe; because the compiler cannot see these
 // values it has to keep the multiply-add form.
 struct Consts {
+    uint32_t ans_bits, ans_mask;             // rANS: probability precision of the layer's table and 2^bits - 1
     uint32_t one, eight, entry, shift16;     // entry = bytes between consecutive fast-table entries (4 * copies);
                                              // shift16 = 65536 (a left shift by 16 as a multiply)
 };
@@ -87,6 +88,7 @@ struct Consts {
 constexpr int kPreparedBytes = kPairEntries * 4 + kExactBytes;
 
 static_assert(sizeof(HuffTables) <= kExactBytes && sizeof(AnsTables) <= kExactBytes, "exact tables do not fit");
+static_assert((4 << kAnsBitsMax) * kCopies <= kLutBytes, "the largest rANS table does not fit the fast-table region");
 
 __device__ int g_staged_status = 0;            // 0 = fine; otherwise the last failure code
 
@@ -553,13 +555,13 @@ struct HuffStaged {
 struct AnsLane {
     uint32_t lo, hi, nx;     // state, byte address of the next word of this stream
     __device__ __forceinline__ uint32_t symbol(const uint8_t *smem, const Consts &k, uint32_t copy_off, uint32_t alim) {
-        if (hi == 0 && lo < (1u << kAnsBits)) {
+        if (hi == 0 && lo <= k.ans_mask) {
             hi = lo;
             lo = *reinterpret_cast<const uint32_t *>(smem + nx);
             nx = min(nx + 256u, alim);
         }
-        const uint32_t e = *reinterpret_cast<const uint32_t *>(smem + umad(lo & kAnsMask, k.entry, copy_off));
-        const uint32_t shifted = __funnelshift_r(lo, hi, kAnsBits);      // state >> 8, fits 32 bits
+        const uint32_t e = *reinterpret_cast<const uint32_t *>(smem + umad(lo & k.ans_mask, k.entry, copy_off));
+        const uint32_t shifted = __funnelshift_r(lo, hi, k.ans_bits);    // state >> bits, fits 32 bits
         const uint64_t next = static_cast<uint64_t>((e >> 12) & 0xFFFu) * shifted + (e & 0xFFFu);
         lo = static_cast<uint32_t>(next);
         hi = static_cast<uint32_t>(next >> 32);
@@ -597,8 +599,8 @@ template <> struct StagedOf<AnsCodec> { using type = AnsStaged; };
 
 __device__ __forceinline__ void build_fast_table(uint32_t *fast, const HuffTables &t, int tid, int n) { build_pair_table(fast, t, tid, n); }
 __device__ __forceinline__ void build_fast_table(uint32_t *fast, const AnsTables &t, int tid, int n) {
-    for (int i = tid; i < (1 << kAnsBits); i += n) {
-        const uint32_t e = t.slot[i];
+    for (int i = tid; i < (1 << t.bits); i += n) {
+        const uint32_t e = __ldg(t.lut + i);
         *reinterpret_cast<uint4 *>(fast + i * kCopies) = make_uint4(e, e, e, e);
     }
 }
@@ -916,7 +918,8 @@ static int staged_launch(const Layer &L, const typename Codec::Args &targs, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() ? 1 : 0;
-    const Consts k{1u, 8u, 4u * kCopies, 65536u};
+    const uint32_t ans_bits = ans_bits_of(targs);
+    const Consts k{ans_bits, (1u << ans_bits) - 1u, 1u, 8u, 4u * kCopies, 65536u};
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, L, targs, prepared, sink, x_bytes, ring_bytes, k, part_bytes, split);
     return e == cudaSuccess ? BHI_OK : cuda_fail(e, "staged kernel launch");
 }

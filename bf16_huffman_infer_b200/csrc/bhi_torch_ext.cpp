@@ -139,6 +139,16 @@ void boxed_huffman_table_hint(StableIValue *stack, uint64_t, uint64_t) {
     check(bhi_huffman_table_hint(ptr<const uint8_t>(blob), static_cast<int>(iarg(stack, 1))));
 }
 
+// Probability precision of an rANS table: it has 2^precision slots (the operator schemas carry no such argument).
+int ans_precision_of(const Tensor &lut) {
+    const int64_t n = lut.numel();
+    int p = 0;
+    while ((int64_t{1} << p) < n) p++;
+    STD_TORCH_CHECK((int64_t{1} << p) == n && p >= BHI_ANS_PRECISION && p <= BHI_ANS_MAX_PRECISION,
+                    "LUT must have 2^precision entries, 8 <= precision <= 12");
+    return p;
+}
+
 // gemv_bf16_huffman_prepared(A_rem, A_exp, X, Y(a!), offsets, prepared) -> ()
 void boxed_gemv_bf16_huffman_prepared(StableIValue *stack, uint64_t, uint64_t) {
     Tensor rem = arg(stack, 0), exp = arg(stack, 1), X = arg(stack, 2), Y = arg(stack, 3), off = arg(stack, 4),
@@ -188,7 +198,7 @@ void boxed_gemv_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
     same_device(rem, X, "X");
     same_device(rem, Y, "Y");
     same_device(rem, lut, "LUT");
-    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int precision = ans_precision_of(lut);
     const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
     STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
     const int64_t B = X.numel() / K;
@@ -196,7 +206,7 @@ void boxed_gemv_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
     STD_TORCH_CHECK(Y.numel() == B * v.M, "Y must be [batch, M]");
     torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
     check(bhi_gemv_bf16_ans(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
-                            ptr<uint16_t>(Y), ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc,
+                            ptr<uint16_t>(Y), ptr<const int32_t>(off), ptr<const uint32_t>(lut), precision, v.S, v.M, v.Nc,
                             static_cast<int>(B), stream_of(rem)));
 }
 
@@ -234,7 +244,7 @@ void boxed_linear_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
     same_device(rem, X, "X");
     same_device(rem, Y, "Y");
     same_device(rem, lut, "LUT");
-    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int precision = ans_precision_of(lut);
     const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
     STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
     const int64_t B = X.numel() / K;
@@ -242,7 +252,7 @@ void boxed_linear_bf16_ans(StableIValue *stack, uint64_t, uint64_t) {
     STD_TORCH_CHECK(Y.numel() == B * v.M, "Y must be [batch, M]");
     torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
     check(bhi_linear_bf16_ans(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
-                              ptr<uint16_t>(Y), ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc,
+                              ptr<uint16_t>(Y), ptr<const int32_t>(off), ptr<const uint32_t>(lut), precision, v.S, v.M, v.Nc,
                               static_cast<int>(B), stream_of(rem)));
 }
 
@@ -299,7 +309,7 @@ void boxed_gemv_bf16_ans_exchange(StableIValue *stack, uint64_t, uint64_t) {
     want(lut, ScalarType::Int, "LUT");
     same_device(rem, X, "X");
     same_device(rem, lut, "LUT");
-    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int precision = ans_precision_of(lut);
     const int64_t K = static_cast<int64_t>(v.S) * v.Nc;
     STD_TORCH_CHECK(X.numel() % K == 0, "X must hold whole rows of split_k*Nc values");
     const int64_t B = X.numel() / K;
@@ -307,7 +317,7 @@ void boxed_gemv_bf16_ans_exchange(StableIValue *stack, uint64_t, uint64_t) {
     const bhi_exchange_t ex = exchange_of(peers, iarg(stack, 6), iarg(stack, 7), iarg(stack, 8));
     torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
     check(bhi_gemv_bf16_ans_exchange(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<const uint16_t>(X),
-                                     ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc, static_cast<int>(B),
+                                     ptr<const int32_t>(off), ptr<const uint32_t>(lut), precision, v.S, v.M, v.Nc, static_cast<int>(B),
                                      &ex, stream_of(rem)));
 }
 
@@ -319,11 +329,11 @@ void boxed_ans_decode(StableIValue *stack, uint64_t, uint64_t) {
     want(lut, ScalarType::Int, "LUT");
     same_device(rem, Y, "Y");
     same_device(rem, lut, "LUT");
-    STD_TORCH_CHECK(lut.numel() == (1 << BHI_ANS_PRECISION), "LUT must have 256 entries");
+    const int precision = ans_precision_of(lut);
     STD_TORCH_CHECK(Y.numel() == static_cast<int64_t>(v.S) * v.M * v.Nc, "Y must be [M, split_k*Nc]");
     torch::stable::accelerator::DeviceGuard guard(rem.get_device_index());
     check(bhi_ans_decode(ptr<const uint8_t>(rem), ptr<const uint32_t>(exp), v.exp_words, ptr<uint16_t>(Y),
-                         ptr<const int32_t>(off), ptr<const uint32_t>(lut), v.S, v.M, v.Nc, stream_of(rem)));
+                         ptr<const int32_t>(off), ptr<const uint32_t>(lut), precision, v.S, v.M, v.Nc, stream_of(rem)));
 }
 
 // huffman_encode(data, LUT, output(a!), output_lengths(b!)) -> ()

@@ -54,6 +54,19 @@ def set_huffman_tables(method: str) -> str:
     previous, HUFFMAN_TABLES = HUFFMAN_TABLES, method
     return previous
 
+
+def set_ans_precision(bits: int) -> int:
+    """Probability precision (8..12 bits) of the rANS models built by later ``ANSWeight.compress`` calls; returns the
+    previous value.  8 is the reference's constant (``functional.py:16``) and what its kernels read; a finer model
+    codes the exponents in fewer words but needs a ``2^bits``-word table per weight, which only this package's kernels
+    accept (the record and table-word formats are unchanged)."""
+    global ANS_PRECISION
+    if not 8 <= int(bits) <= 12:
+        raise ValueError("rANS precision must be in [8, 12]")
+    previous, ANS_PRECISION = ANS_PRECISION, int(bits)
+    return previous
+
+
 __all__ = [
     "linear_huffman",
     "linear_ans",
@@ -65,6 +78,7 @@ __all__ = [
     "convert",
     "fuse_sibling_linears",
     "set_huffman_tables",
+    "set_ans_precision",
 ]
 
 # projections that read the same input inside one block of the usual decoder architectures
@@ -342,9 +356,9 @@ class HuffmanWeight(nn.Module):
 
 
 class ANSWeight(HuffmanWeight):
-    """A ``[M, K]`` BF16 weight with rANS-coded exponents (8-bit probabilities).
+    """A ``[M, K]`` BF16 weight with rANS-coded exponents (8-bit probabilities unless :func:`set_ans_precision` says otherwise).
 
-    Buffers: ``rem``, ``exp``, ``offsets`` as for :class:`HuffmanWeight`, and ``LUT`` i32 ``[256]`` holding
+    Buffers: ``rem``, ``exp``, ``offsets`` as for :class:`HuffmanWeight`, and ``LUT`` i32 ``[2^precision]`` holding
     ``sym << 24 | freq << 12 | (slot - cum[sym])`` per slot (reference ``functional.py:245-310``).
     """
 
@@ -375,6 +389,8 @@ class ANSWeight(HuffmanWeight):
 
     @classmethod
     def get_lut_kwargs(cls, codec: RANSEncoder) -> Dict[str, Tensor]:
+        if max(codec.freq) > 0xFFF:
+            raise ValueError("one exponent value holds the whole 12-bit model: its frequency does not fit the table word")
         lut = torch.tensor(codec.decode_lut, dtype=torch.int32)
         return {"LUT": (lut[:, 0] << 24) | (lut[:, 1] << 12) | lut[:, 2]}
 

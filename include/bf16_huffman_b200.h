@@ -35,7 +35,8 @@ extern "C" {
 #define BHI_MAX_BATCH 8            /* rows of X the fused GEMV accepts */
 #define BHI_MAX_PEERS 8            /* ranks one exchange entry point can serve */
 #define BHI_MAX_LINEAR_BATCH 128   /* rows of X the fused tensor-core product accepts */
-#define BHI_ANS_PRECISION 8
+#define BHI_ANS_PRECISION 8        /* the reference's probability precision (2^8 table slots) */
+#define BHI_ANS_MAX_PRECISION 12   /* largest precision the kernels take (the table word has 12-bit fields) */
 
 /* Message describing the last error returned on this thread ("" if none). */
 const char *bhi_last_error(void);
@@ -113,15 +114,18 @@ int bhi_huffman_decode_prepared(const uint8_t *A_rem, const uint32_t *A_exp, int
                                 uint16_t *Y, const int32_t *offsets, const uint8_t *prepared,
                                 int split_k, int M, int Nc, void *stream);
 
-/* Same two operations for the rANS-coded form; LUT is u32[256] with
- * sym<<24 | freq<<12 | (slot - cum[sym]).
+/* Same two operations for the rANS-coded form; LUT is u32[2^precision] with
+ * sym<<24 | freq<<12 | (slot - cum[sym]), BHI_ANS_PRECISION (8, the reference's constant) <= precision <=
+ * BHI_ANS_MAX_PRECISION (12, what the 12-bit fields of the word allow; the reference's kernel asserts the
+ * same bound, src/kernel.cu:695).  The encoders below take the precision from the model itself
+ * (its frequencies sum to 2^precision).
  * Replace torch.ops.bf16_huffman_infer.gemv_bf16_ans (src/kernel.cu:714-764, schema .cpp:33)
  * and torch.ops.bf16_huffman_infer.ans_decode (src/kernel.cu:878-919, schema .cpp:35). */
 int bhi_gemv_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                      const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                       int split_k, int M, int Nc, int batch, void *stream);
 int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                   uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                    int split_k, int M, int Nc, void *stream);
 
 /* ---- fused decode + tensor-core product for up to 128 rows of X -----------------------------
@@ -141,7 +145,7 @@ int bhi_linear_bf16_huffman_prepared(const uint8_t *A_rem, const uint32_t *A_exp
                                      const uint16_t *X, uint16_t *Y, const int32_t *offsets,
                                      const uint8_t *prepared, int split_k, int M, int Nc, int batch, void *stream);
 int bhi_linear_bf16_ans(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT,
+                        const uint16_t *X, uint16_t *Y, const int32_t *offsets, const uint32_t *LUT, int precision,
                         int split_k, int M, int Nc, int batch, void *stream);
 
 /* ---- row-sharded GEMV with the all-gather in its epilogue --------------------------------------
@@ -173,7 +177,7 @@ int bhi_gemv_bf16_huffman_exchange(const uint8_t *A_rem, const uint32_t *A_exp, 
                                    const uint16_t *X, const int32_t *offsets, const uint8_t *prepared,
                                    int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
 int bhi_gemv_bf16_ans_exchange(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
-                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT,
+                               const uint16_t *X, const int32_t *offsets, const uint32_t *LUT, int precision,
                                int split_k, int M, int Nc, int batch, const bhi_exchange_t *exchange, void *stream);
 
 /* Single-GPU form of bhi_gemv_bf16_huffman_exchange whose counter words live inside the library

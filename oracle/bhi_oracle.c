@@ -30,7 +30,12 @@
 #endif
 
 #define SLAB_ROWS 4096
-#define ANS_BITS 8
+/* Probability precision of the rANS model in use: the reference fixes 8 (functional.py:16, kernel.cu:25); its table
+ * word and its static_assert (kernel.cu:647-649, :695) allow up to 12.  Set before a call, read-only during it. */
+static int ANS_BITS = 8;
+void bhi_oracle_set_ans_bits(int bits) {
+    if (bits >= 8 && bits <= 12) ANS_BITS = bits;
+}
 
 /* ---- byte split / merge: bf16_huffman_infer/utils.py:7-12, src/kernel.cu:149-160 ---------- */
 static inline uint8_t exp_of(uint16_t b) { return (uint8_t)((b >> 7) & 0xFF); }
@@ -142,7 +147,7 @@ void bhi_oracle_huffman_emit(const uint16_t *W, int M, int K, int S, const uint8
  * emitted words are reversed at the end.  Returns the word count; out may be NULL (size pass). */
 static int ans_encode_stream(const uint8_t *sym, int n, const uint32_t *freq, const uint32_t *cum,
                              uint32_t *out /*capacity 8n*/) {
-    uint64_t state = 1u << ANS_BITS;
+    uint64_t state = 1ull << ANS_BITS;
     int cnt = 0;
     for (int i = n - 1; i >= 0; i--) {
         uint32_t f = freq[sym[i]], c = cum[sym[i]];

@@ -77,6 +77,15 @@ def split(w_bits: np.ndarray):
     return rem, exp
 
 
+def _set_ans_bits(n: int) -> None:
+    """Tell the C oracle the rANS probability precision; ``n`` is the table length ``2^bits`` (or the frequency sum)."""
+    bits = int(n).bit_length() - 1
+    if n != 1 << bits or not 8 <= bits <= 12:
+        raise ValueError(f"rANS table length {n} is not 2^8..2^12")
+    lib().bhi_oracle_set_ans_bits(bits)
+
+
+
 def compress(w_bits: np.ndarray, algo: str, tables: Dict[str, np.ndarray], split_k: Optional[int] = None):
     """Whole-layer encode into the device format.  ``tables`` holds ``code_lengths`` and
     ``code_values`` (Huffman) or ``freq`` and ``cum`` (rANS).  Returns ``rem, exp, offsets, L``."""
@@ -96,6 +105,7 @@ def compress(w_bits: np.ndarray, algo: str, tables: Dict[str, np.ndarray], split
     elif algo == "ans":
         fr = _c(tables["freq"], np.uint32)
         cu = _c(tables["cum"], np.uint32)
+        _set_ans_bits(int(fr.astype(np.int64).sum()))
         l.bhi_oracle_ans_row_words(_p(w), M, K, S, _p(fr), _p(cu), _p(L))
     else:
         raise ValueError(algo)
@@ -127,6 +137,7 @@ def decode(algo: str, rem, exp, offsets, tables) -> np.ndarray:
                                              *[_p(x) for x in t], S, M, Nc, _p(out))
     else:
         lut = _c(tables["LUT"], np.int32).view(np.uint32)
+        _set_ans_bits(lut.size)
         rc = lib().bhi_oracle_ans_decode(_p(rem), _p(exp), C.c_int64(exp.size), _p(offsets), _p(lut), S, M, Nc, _p(out))
     if rc != 0:
         raise RuntimeError(f"oracle decode failed (status {rc})")
@@ -160,6 +171,7 @@ def gemv(algo: str, rem, exp, offsets, tables, x_bits: np.ndarray) -> np.ndarray
                                    S, M, Nc, _p(x), B, _p(y))
     else:
         lut = _c(tables["LUT"], np.int32).view(np.uint32)
+        _set_ans_bits(lut.size)
         rc = lib().bhi_oracle_gemv(1, _p(rem), _p(exp), C.c_int64(exp.size), _p(offsets),
                                    None, None, None, None, None, _p(lut), S, M, Nc, _p(x), B, _p(y))
     if rc != 0:
@@ -184,6 +196,7 @@ def ans_encode_op(data: np.ndarray, freq, cum):
     streams, n = d.shape
     out = np.zeros((streams, 8 * n), np.uint32)
     lens = np.zeros(streams, np.int32)
+    _set_ans_bits(int(np.asarray(freq, np.int64).sum()))
     lib().bhi_oracle_ans_encode_op(_p(d), streams, n, _p(_c(freq, np.uint32)), _p(_c(cum, np.uint32)), _p(out), _p(lens))
     return out.view(np.int32), lens
 

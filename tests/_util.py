@@ -36,11 +36,16 @@ def huffman_tables(hist, method="reference"):
             "code_lengths": enc.code_lengths, "code_values": enc.code_values}, enc
 
 
-def ans_tables(hist):
+def ans_tables(hist, precision=8):
     from bf16_huffman_infer_b200.ans import RANSEncoder
-    enc = RANSEncoder([int(x) for x in hist], precision=8)
+    enc = RANSEncoder([int(x) for x in hist], precision=precision)
     lut = np.array([(s << 24) | (f << 12) | r for s, f, r in enc.decode_lut], dtype=np.uint32)
     return {"freq": np.array(enc.freq, np.uint32), "cum": np.array(enc.cum, np.uint32), "LUT": lut.view(np.int32)}, enc
+
+
+def ans_bits(w):
+    """Probability precision of a rANS weight: its table has ``2^bits`` words."""
+    return int(w["LUT"].numel() if hasattr(w["LUT"], "numel") else len(w["LUT"])).bit_length() - 1
 
 
 def tables_for(algo, hist, method="reference"):
@@ -152,7 +157,7 @@ class Abi:
                                                 p(w["code_lengths"]), S, M, Nc, B, self.stream())
         else:
             rc = self.lib.bhi_gemv_bf16_ans(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
-                                            p(w["offsets"]), p(w["LUT"]), S, M, Nc, B, self.stream())
+                                            p(w["offsets"]), p(w["LUT"]), ans_bits(w), S, M, Nc, B, self.stream())
         self.check(rc)
         return y
 
@@ -171,7 +176,7 @@ class Abi:
                                                   p(w["code_lengths"]), S, M, Nc, B, self.stream())
         else:
             rc = self.lib.bhi_linear_bf16_ans(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(y),
-                                              p(w["offsets"]), p(w["LUT"]), S, M, Nc, B, self.stream())
+                                              p(w["offsets"]), p(w["LUT"]), ans_bits(w), S, M, Nc, B, self.stream())
         self.check(rc)
         return y
 
@@ -188,7 +193,7 @@ class Abi:
                                              S, M, Nc, self.stream())
         else:
             rc = self.lib.bhi_ans_decode(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(y), p(w["offsets"]),
-                                         p(w["LUT"]), S, M, Nc, self.stream())
+                                         p(w["LUT"]), ans_bits(w), S, M, Nc, self.stream())
         self.check(rc)
         return y
 

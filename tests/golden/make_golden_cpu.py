@@ -120,6 +120,28 @@ def main():
     with open(os.path.join(HERE, "ref_streams.json"), "w") as f:
         json.dump(streams, f, separators=(",", ":"))
     print(f"{len(tables)} tables, {len(streams)} streams")
+    finer_ans_models()
+
+
+def finer_ans_models():
+    """``RANSEncoder`` at 10 and 12 probability bits (the reference's class takes any precision; its kernels' table word
+    holds up to 12): scaled frequencies and the blob of a few streams, in ``ref_ans_precision.json``."""
+    rng = np.random.default_rng(1234)
+    out = []
+    for name, h in histograms()[:6]:
+        present = np.flatnonzero(h)
+        p = h[present] / h[present].sum()
+        for bits in (10, 12):
+            ans = RA.RANSEncoder(h.tolist(), precision=bits)
+            for n in (1, 64, 74):
+                sym = rng.choice(present, size=n, p=p).astype(int).tolist()
+                blob = ans.compress(sym)
+                assert [int(x) for x in ans.decompress(blob, n)] == sym
+                out.append({"table": name, "precision": bits, "hist": h.tolist(), "freq": ans.freq, "cum": ans.cum,
+                            "symbols": sym, "ans_blob_hex": blob.hex()})
+    with open(os.path.join(HERE, "ref_ans_precision.json"), "w") as f:
+        json.dump(out, f, separators=(",", ":"))
+    print(f"{len(out)} finer-model streams")
 
 
 if __name__ == "__main__":

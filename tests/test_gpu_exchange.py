@@ -61,7 +61,7 @@ def _launch(abi, algo, w, x, ex):
                                                     p(abi.prepare(w)), S, M, Nc, x.shape[0], C.byref(ex), abi.stream())
     else:
         rc = abi.lib.bhi_gemv_bf16_ans_exchange(p(w["rem"]), p(w["exp"]), C.c_int64(w["exp"].numel()), p(x), p(w["offsets"]),
-                                                p(w["LUT"]), S, M, Nc, x.shape[0], C.byref(ex), abi.stream())
+                                                p(w["LUT"]), 8, S, M, Nc, x.shape[0], C.byref(ex), abi.stream())
     abi.check(rc)
 
 

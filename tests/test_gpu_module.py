@@ -47,6 +47,43 @@ def test_compress_matches_oracle_and_decodes(algo, method, M, K):
                                 if algo == "huffman" else {"rem", "exp", "offsets", "LUT"})
 
 
+@pytest.mark.parametrize("bits", [10, 12])
+def test_finer_ans_model_through_the_python_surface(bits, tmp_path):
+    """set_ans_precision: compress builds a 2^bits-word table, the operators infer the precision from it, the layer is
+    never larger than with 8 bits, and a checkpoint of it loads back."""
+    from bf16_huffman_infer_b200 import ANSWeight, checkpoint, convert_all_linear, set_ans_precision
+    M, K = 384, 4096
+    W = make_weight(M, K, 5)
+    Wb = bits_of(W)
+    base = ANSWeight.compress(W)
+    previous = set_ans_precision(bits)
+    try:
+        cw = ANSWeight.compress(W)
+        model = nn.Sequential(nn.Linear(K, M, bias=False)).to(torch.bfloat16)
+        with torch.no_grad():
+            model[0].weight.copy_(W)
+        convert_all_linear(model, min_out_features=0, algo="ans")
+    finally:
+        assert set_ans_precision(previous) == bits
+    assert cw.LUT.numel() == 1 << bits and cw.exp.numel() <= base.exp.numel()
+    tabs = ans_tables(oracle.histogram(Wb), precision=bits)[0]
+    rem, exp, offsets, _ = oracle.compress(Wb, "ans", tabs)
+    assert (cw.LUT.numpy() == tabs["LUT"]).all() and (cw.exp.numpy() == exp).all() and (cw.offsets.numpy() == offsets).all()
+    cw = cw.to(DEV)
+    assert torch.equal(cw.get_weight().cpu().view(torch.int16), W.view(torch.int16))
+    for B in (1, 8, 24):
+        X = make_input(B, K, B)
+        y = F.linear(X.to(DEV), cw).float().cpu().numpy()
+        assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL
+    path = str(tmp_path / "finer.safetensors")
+    checkpoint.save_compressed(model, path)
+    fresh = nn.Sequential(nn.Linear(K, M, bias=False)).to(torch.bfloat16)
+    checkpoint.load_compressed(fresh, path)
+    assert fresh[0].weight.LUT.numel() == 1 << bits
+    X = make_input(2, K, 3).to(DEV)
+    assert torch.equal(fresh.to(DEV)(X), model.to(DEV)(X))
+
+
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
 def test_linear_hook_both_branches_and_bias(algo):
     from bf16_huffman_infer_b200 import ANSWeight, CompressedLinear, HuffmanWeight

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from _util import (GOLDEN, ROOT, Abi, bits_of, make_input, make_weight, rel_err, tables_for, to_device)
+from _util import (GOLDEN, ROOT, Abi, ans_tables, bits_of, make_input, make_weight, rel_err, tables_for, to_device)
 
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 import oracle  # noqa: E402
@@ -101,6 +101,33 @@ def test_encoder_bytes_match_oracle(abi, algo, M, K, S, seed):
     assert g_exp.numel() == exp.size and (g_exp.cpu().numpy() == exp).all()
 
 
+@pytest.mark.parametrize("bits", [9, 10, 11, 12])
+@pytest.mark.parametrize("M,K,S,seed", [(128, 256, 2, 1), (384, 1024, 1, 4), (4224, 128, 1, 6), (512, 4096, 1, 0),
+                                        (128, 12288, 3, 0)])
+def test_finer_ans_models(abi, bits, M, K, S, seed):
+    """rANS with 9..12 probability bits (table of 2^bits words): encoder bytes, decoded weight and the fused product on
+    every kernel path against the oracle run at the same precision."""
+    W = make_weight(M, K, seed)
+    Wb = bits_of(W)
+    tabs = ans_tables(oracle.histogram(Wb), precision=bits)[0]
+    rem, exp, offsets, L = oracle.compress(Wb, "ans", tabs, split_k=S)
+    g_rem, g_exp, g_off, g_rows = abi.encode("ans", W.to(DEV), S, tabs)
+    assert (g_rows.cpu().numpy() == L).all() and (g_off.cpu().numpy() == offsets).all()
+    assert (g_rem.cpu().numpy() == rem).all()
+    assert g_exp.numel() == exp.size and (g_exp.cpu().numpy() == exp).all()
+    w = to_device(dict(rem=rem, exp=exp, offsets=offsets, LUT=tabs["LUT"]), DEV)
+    for path, warps in PATHS:
+        with use_path(abi, path, warps):
+            assert (bits_of(abi.decode("ans", w).cpu()) == Wb).all(), "decoded weight is not bit-exact"
+            for B in (1, 3, 8):
+                X = make_input(B, K, seed)
+                y = abi.gemv("ans", w, X.to(DEV)).float().cpu().numpy()
+                assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL, (path, warps, B)
+    X = make_input(24, K, seed + 1)
+    y = abi.linear("ans", w, X.to(DEV)).float().cpu().numpy()
+    assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL
+
+
 def test_pathological_tables_long_codes(abi):
     """A wide exponent spread (std 1 weights scaled per row) gives codes beyond 16 bits: the third and
     fourth byte tables must work in both paths."""
@@ -156,11 +183,14 @@ def test_argument_errors_are_reported(abi):
     import ctypes as C
     z = torch.zeros(64, dtype=torch.int32, device=DEV)
     rc = abi.lib.bhi_gemv_bf16_ans(abi.p(z), abi.p(z), C.c_int64(64), abi.p(z), abi.p(z), abi.p(z), abi.p(z),
-                                   1, 128, 100, 1, abi.stream())
+                                   8, 1, 128, 100, 1, abi.stream())
     assert rc == 1 and b"multiple of 128" in abi.lib.bhi_last_error()
     rc = abi.lib.bhi_gemv_bf16_ans(abi.p(z), abi.p(z), C.c_int64(64), abi.p(z), abi.p(z), abi.p(z), abi.p(z),
-                                   1, 128, 128, 9, abi.stream())
+                                   8, 1, 128, 128, 9, abi.stream())
     assert rc == 1 and b"batch" in abi.lib.bhi_last_error()
+    rc = abi.lib.bhi_gemv_bf16_ans(abi.p(z), abi.p(z), C.c_int64(64), abi.p(z), abi.p(z), abi.p(z), abi.p(z),
+                                   13, 1, 128, 128, 1, abi.stream())
+    assert rc == 1 and b"precision" in abi.lib.bhi_last_error()
 
 
 REF_LAYOUT = sorted(f for f in os.listdir(GOLDEN) if f.startswith("ref_layout_") and f.endswith(".npz"))

@@ -64,6 +64,41 @@ def test_ans_stream_words_match_reference(rec):
     assert lens[0] == len(ref) and out.view(np.uint32)[0, : lens[0]].tolist() == ref
 
 
+FINER = load_json("ref_ans_precision.json")
+
+
+@pytest.mark.parametrize("rec", FINER, ids=[f"{r['table']}-p{r['precision']}-{len(r['symbols'])}" for r in FINER])
+def test_ans_finer_models_match_reference(rec):
+    """10- and 12-bit probability models: scaled frequencies and stream words equal the reference class's."""
+    bits = rec["precision"]
+    tabs, enc = ans_tables(rec["hist"], precision=bits)
+    assert enc.freq == rec["freq"] and enc.cum == rec["cum"] and tabs["LUT"].size == 1 << bits
+    sym = rec["symbols"]
+    blob = bytes.fromhex(rec["ans_blob_hex"])
+    ref = [int.from_bytes(blob[i:i + 4], "big") for i in range(0, len(blob), 4)][::-1]
+    while len(ref) > 1 and ref[0] == 0:
+        ref.pop(0)
+    got = oracle.py_ans_encode_stream(sym, tabs["freq"], tabs["cum"], bits=bits)
+    assert got == ref
+    assert oracle.py_ans_decode_stream(got, len(sym), tabs["LUT"].view(np.uint32), bits=bits) == sym
+    out, lens = oracle.ans_encode_op(np.array([sym], np.uint8), tabs["freq"], tabs["cum"])
+    assert lens[0] == len(ref) and out.view(np.uint32)[0, : lens[0]].tolist() == ref
+
+
+@pytest.mark.parametrize("bits", [10, 12])
+@pytest.mark.parametrize("M,K,S,seed", [(128, 512, 1, 0), (128, 384, 3, 3), (4100, 128, 1, 4)])
+def test_oracle_roundtrip_finer_ans_models(bits, M, K, S, seed):
+    W = bits_of(make_weight(M, K, seed))
+    hist = oracle.histogram(W)
+    tabs = ans_tables(hist, precision=bits)[0]
+    rem, exp, offsets, _ = oracle.compress(W, "ans", tabs, split_k=S)
+    assert (oracle.decode("ans", rem, exp, offsets, tabs) == W).all()
+    x = bits_of(make_input(2, K, seed))
+    assert np.allclose(oracle.gemv("ans", rem, exp, offsets, tabs, x), oracle.matvec(W, x), rtol=0, atol=1e-3)
+    _, exp8, _, _ = oracle.compress(W, "ans", tables_for("ans", hist), split_k=S)
+    assert K < 384 or exp.size <= exp8.size      # two-symbol streams are all flush: no model helps there
+
+
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
 @pytest.mark.parametrize("M,K,S,seed", [(128, 512, 1, 0), (128, 512, 2, 1), (256, 1024, 1, 2), (128, 384, 3, 3),
                                         (4100, 128, 1, 4)])
