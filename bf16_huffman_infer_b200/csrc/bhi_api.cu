@@ -10,7 +10,7 @@
 #include "bhi_generic.cuh"
 #include "bhi_staged.cuh"
 #include "bhi_quad.cuh"
-#include "bhi_gemm.cuh"
+#include "bhi_tile.cuh"
 
 namespace bhi {
 
@@ -136,7 +136,7 @@ static int run_linear(const Layer &L, const typename Codec::Args &targs, const u
     BHI_REQUIRE(B >= 1 && B <= BHI_MAX_LINEAR_BATCH, "batch must be in [1, 128]");
     BHI_REQUIRE(aligned(X, 16) && aligned(Y, 2), "activation buffers must be 16-byte (X) / 2-byte (Y) aligned");
     BHI_REQUIRE(aligned(L.rem, 16) && aligned(L.exp, 16) && aligned(prepared, 16), "weight buffers must be 16-byte aligned");
-    return gemm_launch<Codec>(L, targs, prepared, X, Y, B, st);
+    return tile_launch<Codec>(L, targs, prepared, X, Y, B, st);
 }
 
 template <class Codec>
