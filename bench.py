@@ -571,6 +571,15 @@ def main():
     ap.add_argument("--no-70b", action="store_true", help="skip the Llama-3-70B-shape stack")
     args = ap.parse_args()
 
+    # The contract is ONE line on stdout.  Libraries write there too (NCCL prints its version when its first communicator
+    # comes up): everything but the result line goes to stderr.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(result_fd, (json.dumps(obj) + "\n").encode())
+
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -586,7 +595,7 @@ def main():
             per_step.append(step_seconds)
         step_seconds = float(np.median(per_step))
         base["value"] = args.batch / step_seconds
-        print(json.dumps({
+        emit({
             "metric": "decode tokens/s (hot path: all compressed linear layers of one token)", "value": base["value"],
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(per_step), "warmup": 0, "ms_per_step": step_seconds * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 weights, fp32 accumulate",
@@ -596,7 +605,7 @@ def main():
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
-        }))
+        })
         return
 
     assert torch.cuda.is_available(), "bench.py --impl ours needs a CUDA device (there is no CPU fallback)"
@@ -651,7 +660,7 @@ def main():
             line["reference_gpu"] = reference_gpu_arm(args.batch)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_arm(args.workload, args.algo, args.batch, tables=args.tables, ans_precision=args.ans_precision)
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
