@@ -11,6 +11,7 @@
 #include "bhi_staged.cuh"
 #include "bhi_quad.cuh"
 #include "bhi_tile.cuh"
+#include "bhi_tileq.cuh"
 
 namespace bhi {
 
@@ -136,6 +137,10 @@ static int run_linear(const Layer &L, const typename Codec::Args &targs, const u
     BHI_REQUIRE(B >= 1 && B <= BHI_MAX_LINEAR_BATCH, "batch must be in [1, 128]");
     BHI_REQUIRE(aligned(X, 16) && aligned(Y, 2), "activation buffers must be 16-byte (X) / 2-byte (Y) aligned");
     BHI_REQUIRE(aligned(L.rem, 16) && aligned(L.exp, 16) && aligned(prepared, 16), "weight buffers must be 16-byte aligned");
+    if (g_path.load() != 2) {
+        const int rc = tileq_launch<Codec>(L, targs, prepared, X, Y, B, st);
+        if (rc != kStagedDeclined) return rc;
+    }
     return tile_launch<Codec>(L, targs, prepared, X, Y, B, st);
 }
 

@@ -32,9 +32,9 @@ ANS_PRECISION = 8
 SLAB_ROWS = 4096          # rows encoded per slab; 64 padding words follow every slab
 FUSED_MAX_ROWS = 8        # up to here: fused decode + GEMV; beyond: decode, then a library GEMM (as the reference)
 # Rows up to which the fused decode + tensor-core product (mm_huffman_prepared / mm_ans, at most 128) is used
-# instead of decode + GEMM.  Off by default: on B200 it is correct but not faster than decode + library GEMM (it runs
-# at the speed of its in-register stream decoders: 31 / 62 / 83 us against 23 / 61 / 63 us on the 4096x4096,
-# 12288x4096 and 4096x12288 layers at 16 rows).  BHI_TENSOR_ROWS=128 turns it on.
+# instead of decode + GEMM.  Off by default: on B200 it is within 5 % of decode + library GEMM up to 32 rows and
+# behind it beyond (python -m bf16_huffman_infer_b200.examples.linear_bench), but needs no dense scratch.
+# BHI_TENSOR_ROWS=32 (or up to 128) turns it on.
 TENSOR_MAX_ROWS = int(os.environ.get("BHI_TENSOR_ROWS", "0"))
 # Which prefix code HuffmanWeight.compress builds (huffman.py; every choice yields tables of the reference's
 # format, readable by any decoder of it, the reference's included):

@@ -53,19 +53,47 @@ SHAPES = [
 ]
 
 
+# the two fused tensor-core kernels: path 0 = records staged in shared memory while the batch leaves room for them (up to
+# about 48 rows), streams in registers beyond; path 2 = streams in registers at every batch
+@pytest.mark.parametrize("path", [0, 2], ids=["staged", "registers"])
 @pytest.mark.parametrize("prepared", [False, True], ids=["tables", "prepared"])
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
 @pytest.mark.parametrize("M,K,S,seed", SHAPES)
-def test_linear_matches_oracle(abi, prepared, algo, M, K, S, seed):
+def test_linear_matches_oracle(abi, path, prepared, algo, M, K, S, seed):
     if prepared and algo == "ans":
         pytest.skip("prepared tables exist for the Huffman coder only")
     Wb, w = _device_layer(algo, M, K, S, seed)
-    for B in (9, 16, 33, 64, 100, 128, 1):
-        X = make_input(B, K, seed + B)
-        y = abi.linear(algo, w, X.to(DEV), prepared=prepared).float().cpu().numpy()
-        ref = oracle.matvec(Wb, bits_of(X))
-        assert rel_err(y, ref) <= TOL, (B, rel_err(y, ref))
-    assert _status(abi) == 0, "a bounded wait expired inside the kernel"
+    previous = abi.set_path(path)
+    try:
+        for B in (9, 16, 24, 33, 48, 64, 100, 128, 1):
+            X = make_input(B, K, seed + B)
+            y = abi.linear(algo, w, X.to(DEV), prepared=prepared).float().cpu().numpy()
+            ref = oracle.matvec(Wb, bits_of(X))
+            assert rel_err(y, ref) <= TOL, (B, rel_err(y, ref))
+        assert _status(abi) == 0, "a bounded wait expired inside the kernel"
+    finally:
+        abi.set_path(previous)
+
+
+@pytest.mark.parametrize("path", [0, 2], ids=["staged", "registers"])
+@pytest.mark.parametrize("method", ["limit6", "escape"])
+@pytest.mark.parametrize("M,K,S", [(200, 4736, 1), (96, 4736 * 4, 4), (4224, 384, 3)])
+def test_linear_other_tables_and_odd_block_counts(abi, path, method, M, K, S):
+    """Tables without unresolved windows take the branch-free loops; 37 blocks per chunk end on half a stage pair."""
+    W = make_weight(M, K, 21, 0.02)
+    Wb = bits_of(W)
+    tabs = tables_for("huffman", oracle.histogram(Wb), method)
+    rem, exp, offsets, _ = oracle.compress(Wb, "huffman", tabs, split_k=S)
+    w = to_device(dict(rem=rem, exp=exp, offsets=offsets, **{k: v for k, v in tabs.items() if k != "code_values"}), DEV)
+    previous = abi.set_path(path)
+    try:
+        for B in (12, 32, 72):
+            X = make_input(B, K, B)
+            y = abi.linear("huffman", w, X.to(DEV), prepared=True).float().cpu().numpy()
+            assert rel_err(y, oracle.matvec(Wb, bits_of(X))) <= TOL, B
+        assert _status(abi) == 0
+    finally:
+        abi.set_path(previous)
 
 
 @pytest.mark.parametrize("algo", ["huffman", "ans"])
