@@ -17,11 +17,14 @@
 //
 // Measured on B200 (16 rows of X; 4096 x 4096 / 12288 x 4096 / 4096 x 12288): 23.6 / 60.8 / 59.8 us, against 22.5 / 59.3 /
 // 62.1 us for decode-to-dense + library GEMM and 32.7 / 64.9 / 88.3 us for tile_kernel.  Without its MMAs (results wrong)
-// the same kernel takes 17.1 us on the first shape: the decoders run at the GEMV kernel's pace, and the 256 MMAs of a
-// CTA's set add their issue time (0.44 us per stage of 16) on top instead of hiding behind the decoders.  Tried without
-// effect on that: M = 64 instead of 128, three W stages, up to eight X stages, polling instead of parked waits, the 8
-// MMAs of a block as one piece of inline assembly, four issuer warps (one per scheduler) taking the stages in turn
-// (slower: 25.6 us).  Tensor pipe 8 % busy, shared-memory data pipe 35 %, issue slots 26 %.
+// the same kernel takes 17.1 us on the first shape: the decoders run at the GEMV kernel's pace.  What holds it back is the
+// issue rate of tcgen05.mma while the decoders run: with the issuer and the decoders uncoupled (no waits between them,
+// results wrong) the 256 MMAs of a CTA's set take 16.5 us, 64 ns (122 clocks) each against 52 clocks on an idle SM, whatever
+// N (8 or 32) and M (64 or 128).  At 8 MMAs per block of 32 rows that is 0.51 us against 0.38 us of decoding.  Tried without
+// effect: three W stages, up to eight X stages, polling instead of parked waits, the 8 MMAs of a block as one piece of
+// inline assembly, a scheduler without decoder warps for the issuer, four issuer warps (one per scheduler) taking the
+// stages in turn (slower: 25.6 us).  Tensor pipe 8 % busy, shared-memory data pipe 35 %, issue slots 26 %.  Fewer, larger
+// MMAs need more rows per set, and a set's records must fit the rings.
 #pragma once
 
 #include "bhi_quad.cuh"
