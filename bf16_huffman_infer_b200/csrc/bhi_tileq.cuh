@@ -15,7 +15,7 @@
 // 64 + 2 sigma, 65 + 2 sigma.  W stage layout: 16-byte units at unit index kc * 36 + row (kc = K-chunk of 8 columns), so
 // the 32 lanes of a store hit 32 different banks.
 //
-// Measured on B200 (16 rows of X; 4096 x 4096 / 12288 x 4096 / 4096 x 12288): 23.6 / 60.8 / 59.8 us, against 22.5 / 59.3 /
+// Measured on B200 (16 rows of X; 4096 x 4096 / 12288 x 4096 / 4096 x 12288): 23.2 / 60.3 / 59.4 us, against 22.5 / 59.3 /
 // 62.1 us for decode-to-dense + library GEMM and 32.7 / 64.9 / 88.3 us for tile_kernel.  Without its MMAs (results wrong)
 // the same kernel takes 17.1 us on the first shape: the decoders run at the GEMV kernel's pace.  What holds it back is the
 // issue rate of tcgen05.mma while the decoders run: with the issuer and the decoders uncoupled (no waits between them,
@@ -71,9 +71,8 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
     const uint32_t smem_base = smem_addr(smem);
     const uint32_t table_bar = smem_addr(&bars[16]);
     const uint32_t full_bar = smem_addr(&bars[17]);        // + 8 * W stage
-    const uint32_t empty_bar = smem_addr(&bars[20]);       // + 8 * W stage (room for three)
     const uint32_t xfull_bar = smem_addr(&bars[23]);       // + 8 * X stage
-    const uint32_t xempty_bar = smem_addr(&bars[31]);      // + 8 * X stage
+    const uint32_t sdone_bar = smem_addr(&bars[31]);       // + 8 * (stage number % 8): the stage's MMAs are complete
     const uint32_t done_bar = smem_addr(&bars[39]);        // + 8 * accumulator
     const uint32_t free_bar = smem_addr(&bars[41]);        // + 8 * accumulator
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(&bars[43]);
@@ -93,11 +92,10 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
         for (int g = 0; g < 2 * kQuadGroups; g++) mbar_init(smem_addr(&bars[g]), 1);
         for (int s = 0; s < kTqWStages; s++) {
             mbar_init(full_bar + 8 * s, kTqDecoders);
-            mbar_init(empty_bar + 8 * s, 1);
         }
         for (int s = 0; s < kTqXStagesMax; s++) {
             mbar_init(xfull_bar + 8 * s, 1);
-            mbar_init(xempty_bar + 8 * s, 1);
+            mbar_init(sdone_bar + 8 * s, 1);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(done_bar + 8 * a, 1);
@@ -250,10 +248,13 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
         // this lane's word of pass 0, block half 0, inside a W stage: row 4 group + r, K-chunk 4 wig + (j >> 2), word j & 3
         const uint32_t j8 = lane & 7;
         const uint32_t ws_lane = P.w_off + (((4u * wig + (j8 >> 2)) * kTqLbo + 4u * group + r) * 4u + (j8 & 3u)) * 4u;
-        uint32_t stage = 0u, wraps = 0u;             // position in the W ring; every decoder warp and the issuer walk the same sequence
+        uint32_t stage = 0u, un = 0u;                // slot in the W ring and stage number; every decoder warp and the issuer walk the same sequence
         auto begin_pair = [&]() {
-            // the stage is free once the MMAs that read it kTqWStages pairs ago have completed
-            if (wraps > 0u && !mbar_wait_parked(empty_bar + 8u * stage, (wraps - 1u) & 1u) && lane == 0) atomicExch(&g_staged_status, 3);
+            // the slot is free once the MMAs that read it kTqWStages stages ago have completed
+            if (un >= kTqWStages) {
+                const uint32_t w = un - kTqWStages;
+                if (!mbar_wait_parked(sdone_bar + 8u * (w & 7u), (w >> 3) & 1u) && lane == 0) atomicExch(&g_staged_status, 3);
+            }
         };
         auto emit = [&](int pp, int half, uint32_t rw, uint32_t e0, uint32_t e1) {
             uint8_t *ws = smem + ws_lane + stage * kTqWStage + half * kTqHalf + pp * (2 * kTqLbo * 16);
@@ -264,10 +265,8 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(full_bar + 8u * stage);
-            if (++stage == kTqWStages) {
-                stage = 0u;
-                wraps++;
-            }
+            un++;
+            if (++stage == kTqWStages) stage = 0u;
         };
 
         uint32_t phases = 0u;
@@ -413,9 +412,10 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
                             umma_bf16(acc, ((j >> 2) ? xd1 : xd0) + static_cast<uint64_t>((j & 3) * 2), wd + static_cast<uint64_t>(j * 2 * kTqLbo),
                                       kIdesc, (v | static_cast<uint32_t>(h) | static_cast<uint32_t>(j)) != 0u ? 1u : 0u);
                     }
-                    umma_commit(empty_bar + 8u * s);
-                    umma_commit(xempty_bar + 8u * xs);
+                    // one commit per stage (each costs the issuing thread about 300 clocks): the decoders and the loader wait on the
+                    // same barrier, a ring of eight so that neither can fall two phases behind
                     if (v + 1u == stages_per_set) umma_commit(done_bar + 8u * a);
+                    umma_commit(sdone_bar + 8u * (u & 7u));
                 }
             }
             tc_fence_before();
@@ -425,7 +425,7 @@ tileq_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const
         // ---- loader: X stage u + x_stages as soon as the MMAs of stage u are done ----------------------------------------
         if (lane == 0) {
             for (uint32_t u = 0; u + P.x_stages < my_stages; u++) {
-                if (!mbar_wait_parked(xempty_bar + 8u * (u % P.x_stages), (u / P.x_stages) & 1u)) atomicExch(&g_staged_status, 6);
+                if (!mbar_wait_parked(sdone_bar + 8u * (u & 7u), (u >> 3) & 1u)) atomicExch(&g_staged_status, 6);
                 request_x(u + P.x_stages);
             }
         }
