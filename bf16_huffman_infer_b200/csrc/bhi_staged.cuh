@@ -315,6 +315,9 @@ struct PeerSet {
 __device__ __forceinline__ void red_release_sys_add(uint32_t *p, uint32_t v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t *p, uint32_t v) {
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -374,9 +377,12 @@ __device__ __forceinline__ void exchange_finish(const PeerSet &peers, uint32_t l
             // last CTA of this launch.  The arrival counter goes back to zero for the next launch of the layer,
             // whatever grid that one uses (its CTAs arrive only after this whole grid has completed).
             *reinterpret_cast<volatile uint32_t *>(peers.launches + 1) = 0u;
+            // one system-scope fence, then a relaxed add per peer: a release per peer would be a fence per peer, one after
+            // the other (7 us more per launch on 8 GPUs than on 4)
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
 #pragma unroll
             for (int q = 0; q < kMaxPeers; q++)
-                if (q < peers.world) red_release_sys_add(peers.done[q], 1u);
+                if (q < peers.world) red_relaxed_sys_add(peers.done[q], 1u);
             if (!counter_wait_bounded(pick(peers.done, peers.rank), launch_no * peers.world)) atomicExch(&g_staged_status, 9);
             *peers.launches = launch_no;
             __threadfence();
