@@ -49,6 +49,9 @@ int bhi_abi_version(void);
  *       one-row-per-warp staged kernel, else the generic path)
  *   1 = generic path only (one warp per record, direct global loads)
  *   2 = skip the four-rows-per-warp-group kernel (one-row-per-warp staged kernel, else generic)
+ * The linear entry points choose between their two kernels the same way: 0 = the one whose decoders stage records in
+ * shared memory when the batch leaves room for them (up to about 48 rows), else the one that keeps its streams in
+ * registers; 2 = the latter always.
  * Process-wide; meant for tests and A/B measurements.  Returns the previous value. */
 int bhi_set_kernel_path(int path);
 
@@ -134,8 +137,10 @@ int bhi_ans_decode(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_word
  * the weight to a dense scratch with huffman_decode / ans_decode and calls a library GEMM
  * (bf16_huffman_infer/functional.py:398-407, 469-478).  These entry points replace that pair of
  * calls: a set of weight rows is decoded into shared memory and multiplied there by tcgen05.mma
- * with the accumulator in tensor memory, so the dense weight never reaches HBM.  Accumulation is
- * FP32 over the whole row, one rounding to BF16 at the end.  X must be 16-byte aligned. */
+ * with the accumulator in tensor memory, so the dense weight never reaches HBM and no scratch is
+ * needed.  Accumulation is FP32 over the whole row, one rounding to BF16 at the end.  X must be
+ * 16-byte aligned.  Measured on B200: within 5 % of decode + library GEMM up to 32 rows, behind it
+ * beyond. */
 int bhi_linear_bf16_huffman(const uint8_t *A_rem, const uint32_t *A_exp, int64_t exp_words,
                             const uint16_t *X, uint16_t *Y, const int32_t *offsets,
                             const uint8_t *LUT1, const uint8_t *LUT2, const uint8_t *LUT3,
