@@ -556,8 +556,10 @@ quad_kernel(Layer L, typename Codec::Args targs, const uint8_t *prepared, const 
     }
 
     if (exchange) {
+        // one thread asks whether every peer's buffer may be overwritten (an acquire at system scope); the barrier that
+        // makes the staged results visible hands its answer to the others
+        if (tid == 0 && !counter_wait_bounded(pick(peers.ready, peers.rank), launch_no * peers.world)) atomicExch(&g_staged_status, 8);
         __syncthreads();
-        if (!counter_wait_bounded(pick(peers.ready, peers.rank), launch_no * peers.world) && lane == 0) atomicExch(&g_staged_status, 8);
         for (int i = tid; i < B * rows_cta; i += kThreads) {
             const int b = i / rows_cta, rr = i - b * rows_cta;
             const uint16_t v = ys[i];
