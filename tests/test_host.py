@@ -150,3 +150,38 @@ def test_compressed_checkpoint_roundtrip(tmp_path):
     with pytest.raises(ValueError, match="does not fit"):
         load_compressed(other, path)
     assert isinstance(other.q_proj, torch.nn.Linear)
+
+
+@pytest.mark.parametrize("bits", [10, 12])
+def test_checkpoint_keeps_the_ans_table_size(tmp_path, bits):
+    """A rANS weight built at 10 or 12 probability bits has a 2^bits-word table; the manifest records it, the loader
+    rebuilds a buffer of that size, and the decoded weight (CPU oracle) is unchanged by the trip."""
+    import numpy as np
+    from _util import ans_tables
+    from bf16_huffman_infer_b200 import ANSWeight, CompressedLinear, load_compressed, save_compressed
+    W = make_weight(128, 512, 5)
+    Wb = bits_of(W)
+    tabs = ans_tables(oracle.histogram(Wb), precision=bits)[0]
+    rem, exp, offsets, _ = oracle.compress(Wb, "ans", tabs)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    src = torch.nn.Sequential(torch.nn.Linear(512, 128, bias=False)).to(torch.bfloat16)
+    src[0] = CompressedLinear(ANSWeight(t(rem), t(exp), t(offsets), t(tabs["LUT"])), None)
+    path = str(tmp_path / "ans.safetensors")
+    save_compressed(src, path)
+    dst = load_compressed(torch.nn.Sequential(torch.nn.Linear(512, 128, bias=False)).to(torch.bfloat16), path)
+    w = dst[0].weight
+    assert isinstance(w, ANSWeight) and w.LUT.numel() == 1 << bits
+    back = oracle.decode("ans", w.rem.numpy(), w.exp.numpy(), w.offsets.numpy(), {"LUT": w.LUT.numpy()})
+    assert (back == Wb).all()
+
+
+def test_set_ans_precision_bounds():
+    from bf16_huffman_infer_b200 import set_ans_precision
+    previous = set_ans_precision(12)
+    try:
+        assert set_ans_precision(8) == 12
+        for bad in (7, 13):
+            with pytest.raises(ValueError):
+                set_ans_precision(bad)
+    finally:
+        set_ans_precision(previous)
