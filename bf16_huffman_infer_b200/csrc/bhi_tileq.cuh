@@ -5,7 +5,7 @@
 // warp issues the MMAs, one requests the X blocks by TMA, four read the accumulators back.  What differs is where the
 // decoders get their streams from: here the records of a QUAD (four rows) are copied whole into a two-ended ring by the
 // bulk-copy engine, as in quad_kernel (bhi_quad.cuh), and decoded with its cursor-in-shared-memory loop: two table
-// look-ups per window fetch, 52 instructions per row and 128-column block instead of 73.  Eight groups of two warps hold
+// look-ups per window fetch, 47 to 52 instructions per row and 128-column block instead of 73.  Eight groups of two warps hold
 // eight quads, so a SET is 32 weight rows (MMA N = 32) and a W stage is a PAIR of 128-column blocks (16 MMAs), because
 // one decoder step yields two blocks.  The rings take the shared memory the larger X stages of more than 32 rows would
 // need; beyond that (and for records that do not fit a ring slot pair) tile_kernel runs.
