@@ -56,6 +56,7 @@ WORKLOADS = {
     # name: (layers, hidden, intermediate, q_heads, kv_heads, head_dim, vocab)
     "qwen3-8b": (36, 4096, 12288, 32, 8, 128, 151936),
     "llama3-70b": (80, 8192, 28672, 64, 8, 128, 128256),
+    "qwen2.5-7b": (28, 3584, 18944, 28, 4, 128, 152064),
     "tiny": (2, 1024, 3072, 8, 2, 128, 8192),
 }
 # DRAM bytes read + written per launch / algorithmic bytes of the fused Huffman GEMV, from the ncu capture
