@@ -162,7 +162,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "window": "timed region, then the same replay for 0.5 s"}
 
 
 # ---- the CPU arm (oracle): bounded sample of the workload ------------------------------------------------
@@ -397,6 +397,14 @@ def ours(args, rank, world, dev, light=False):
         graph.replay()
     with ClockSampler(dev.index) as clocks:
         ms = timed_region(graph.replay, steps, world, dev)
+        if not light:
+            # A short timed region (tens of milliseconds at N = 8) ends before nvidia-smi has printed a line: keep the same
+            # load running, untimed, for half a second.  The count comes from the rank-maximum time, so every rank replays
+            # the same number of steps (the exchange kernels need all of them).
+            extra = max(1, int(0.5 / max(ms / steps * 1e-3, 1e-6)))
+            for _ in range(extra):
+                graph.replay()
+            torch.cuda.synchronize()
     ms_e2e = None
     if not light:
         for _ in range(2):
